@@ -1,0 +1,321 @@
+"""Torch-native (CPU) restatement of the reference's block-FP8 algorithms.
+
+TEST INFRASTRUCTURE ONLY -- see ``oracle/__init__.py``.
+
+Each function names the reference source it restates (paths are relative to
+the reference project root):
+
+* ``per_token_group_quant_fp8``  <- ``native_per_token_group_quant_fp8``
+  (test/manual/quant/test_block_fp8.py:41-66) with the CUDA kernels' fp32
+  ``eps`` (sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:45,79-86,110).
+* ``block_quant_weight_fp8``     <- ``convert_weight``
+  (test/registered/cpu/utils.py:53-101).
+* ``w8a8_block_fp8_matmul``      <- ``native_w8a8_block_fp8_matmul``
+  (test/manual/quant/test_block_fp8.py:291-340).
+* ``moe_align_block_size``       <- ``moe_align_block_size_kernel`` +
+  ``count_and_sort_expert_tokens_kernel``
+  (sgl-kernel/csrc/moe/moe_align_kernel.cu:27-41,55-233) and the output sizing
+  of python/sglang/srt/layers/moe/moe_runner/triton_utils/moe_align_block_size.py:58-87,
+  with the stable (ascending flat index) order of the small-batch kernel
+  (moe_align_kernel.cu:309-314).
+* ``silu_and_mul``               <- ``SiluAndMul.forward_native``
+  (python/sglang/srt/layers/activation.py:86-88).
+* ``fused_experts_fp8``          <- ``torch_w8a8_block_fp8_moe``
+  (test/manual/quant/test_block_fp8.py:518-547), taking ``topk_weights`` /
+  ``topk_ids`` as inputs instead of its internal softmax-top-k, skipping ids
+  outside ``[0, E)`` (the expert-parallel "-1" convention of
+  python/sglang/srt/layers/moe/token_dispatcher/standard.py:172-210).
+* ``softmax_topk``               <- ``fused_topk_torch_native``
+  (python/sglang/srt/layers/moe/topk.py:550-588).
+* ``biased_grouped_topk``        <- ``biased_grouped_topk_impl``
+  (python/sglang/srt/layers/moe/topk.py:923-992).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+FP8_MIN = -448.0
+
+__all__ = [
+    "FP8",
+    "FP8_MAX",
+    "per_token_group_quant_fp8",
+    "block_quant_weight_fp8",
+    "w8a8_block_fp8_matmul",
+    "w8a8_block_fp8_linear",
+    "moe_align_sizes",
+    "moe_align_block_size",
+    "silu_and_mul",
+    "fused_experts_fp8",
+    "softmax_topk",
+    "biased_grouped_topk",
+    "ep_local_expert_ids",
+    "rel_frobenius",
+]
+
+
+# --------------------------------------------------------------------------- quant
+def per_token_group_quant_fp8(
+    x: torch.Tensor, group_size: int, eps: float = 1e-10, formula: int = 0
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row, per-``group_size`` FP8 E4M3 quantisation with fp32 scales.
+
+    ``formula`` selects which of the reference's three arithmetic variants is
+    reproduced (all share ``amax = max(|x|, eps)`` over the group, in fp32):
+
+    * 0: ``s = amax / 448``; ``q = x / s``        (torch-native oracle, CUDA v1)
+    * 1: ``s = amax / 448``; ``q = x * (1 / s)``  (Triton row-major kernel,
+         python/sglang/srt/layers/quantization/fp8_kernel.py:180-183)
+    * 2: ``s = amax * (1/448)``; ``q = x * (448 / amax)`` (CUDA v2,
+         sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:69-80)
+
+    Differences from ``native_per_token_group_quant_fp8``: ``eps`` is applied
+    after the upcast to fp32 (as every CUDA kernel of the reference does), which
+    only matters for an all-zero group.
+    """
+    assert x.shape[-1] % group_size == 0
+    assert x.is_contiguous()
+    xf = x.reshape(-1, group_size).to(torch.float32)
+    amax = xf.abs().amax(dim=-1, keepdim=True).clamp(min=eps)
+    if formula == 0:
+        s = amax / FP8_MAX
+        q = xf / s
+    elif formula == 1:
+        s = amax / FP8_MAX
+        q = xf * (1.0 / s)
+    elif formula == 2:
+        s = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32)
+        q = xf * (FP8_MAX / amax)
+    else:
+        raise ValueError(f"unknown formula {formula}")
+    q = q.clamp(min=FP8_MIN, max=FP8_MAX).to(FP8).reshape(x.shape)
+    s = s.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
+    return q, s
+
+
+def block_quant_weight_fp8(
+    w: torch.Tensor, block: Sequence[int] = (128, 128)
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Quantise a ``[N, K]`` weight to FP8 with one fp32 scale per ``block``.
+
+    ``scale = amax / 448`` (1.0 where a block is all zero), ``q = w / scale``.
+    """
+    N, K = w.shape
+    bn, bk = block
+    pn, pk = (-N) % bn, (-K) % bk
+    wf = w.to(torch.float32)
+    if pn or pk:
+        wf = F.pad(wf, (0, pk, 0, pn))
+    nb, kb = wf.shape[0] // bn, wf.shape[1] // bk
+    blocks = wf.view(nb, bn, kb, bk).permute(0, 2, 1, 3)
+    amax = blocks.abs().amax(dim=(-2, -1), keepdim=True)
+    scales = amax / FP8_MAX
+    scales = torch.where(scales == 0, torch.ones_like(scales), scales)
+    q = (blocks / scales).to(FP8).permute(0, 2, 1, 3).reshape(nb * bn, kb * bk)
+    return q[:N, :K].contiguous(), scales.view(nb, kb).contiguous()
+
+
+# ---------------------------------------------------------------------------- GEMM
+def w8a8_block_fp8_matmul(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    As: torch.Tensor,
+    Bs: torch.Tensor,
+    block_size: Sequence[int],
+    output_dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """``C = sum_kb (A_kb @ B_kb^T) * As[:, kb] * Bs[n // bn, kb]``, fp32 accumulate."""
+    A = A.to(torch.float32)
+    B = B.to(torch.float32)
+    bn, bk = block_size
+    assert A.shape[-1] == B.shape[-1] and B.ndim == 2 and Bs.ndim == 2
+    K = A.shape[-1]
+    M = A.numel() // K
+    N = B.shape[0]
+    nt, kt = (N + bn - 1) // bn, (K + bk - 1) // bk
+    assert As.shape[-1] == kt and tuple(Bs.shape) == (nt, kt)
+    out_shape = A.shape[:-1] + (N,)
+    A = A.reshape(M, K)
+    As = As.reshape(M, kt).to(torch.float32)
+    C = torch.zeros(M, N, dtype=torch.float32)
+    for i in range(kt):
+        a = A[:, i * bk : min((i + 1) * bk, K)]
+        for j in range(nt):
+            b = B[j * bn : min((j + 1) * bn, N), i * bk : min((i + 1) * bk, K)]
+            s = As[:, i : i + 1] * Bs[j, i]
+            C[:, j * bn : min((j + 1) * bn, N)] += torch.matmul(a, b.t()) * s
+    return C.reshape(out_shape).to(output_dtype)
+
+
+def w8a8_block_fp8_linear(x, wq, ws, block_size=(128, 128), bias=None, output_dtype=None):
+    """quant(1 x block_k) -> block GEMM -> optional bias; the composition of
+    ``triton_w8a8_block_fp8_linear`` (python/sglang/srt/layers/quantization/fp8_utils.py:814-834)."""
+    output_dtype = output_dtype or x.dtype
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    q, s = per_token_group_quant_fp8(x2, block_size[1])
+    out = w8a8_block_fp8_matmul(q, wq, s, ws, block_size, output_dtype=torch.float32)
+    if bias is not None:
+        out = out + bias.to(torch.float32)
+    return out.to(output_dtype).reshape(x.shape[:-1] + (wq.shape[0],))
+
+
+# --------------------------------------------------------------------------- align
+def moe_align_sizes(numel: int, block_size: int, num_experts: int) -> Tuple[int, int]:
+    """(max_num_tokens_padded, max_num_m_blocks) exactly as the reference sizes its outputs."""
+    if numel < num_experts + 1:
+        max_pad = numel * block_size
+    else:
+        max_pad = numel + (num_experts + 1) * (block_size - 1)
+    return max_pad, (max_pad + block_size - 1) // block_size
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int):
+    """Bucket flat ``topk_ids`` by expert (ids in ``[-1, E)``; bucket 0 is "-1"),
+    pad every bucket to a multiple of ``block_size`` and emit, in bucket order, the
+    flat indices (ascending inside a bucket, ``numel`` in pad slots).
+
+    Returns ``(sorted_ids[max_pad], expert_ids[max_blocks], num_post_pad[1], cumsum[E+2])``.
+    ``expert_ids`` past the last real block is -1; ``cumsum[b]`` is the END of
+    bucket ``b``'s real (unpadded) entries, which is the state the reference's
+    scatter kernel leaves behind; ``cumsum[E+1]`` is the padded total.
+    """
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    numel = flat.numel()
+    nb = num_experts + 1
+    max_pad, max_blocks = moe_align_sizes(numel, block_size, num_experts)
+    sorted_ids = torch.full((max_pad,), numel, dtype=torch.int32)
+    expert_ids = torch.full((max_blocks,), -1, dtype=torch.int32)
+    cumsum = torch.zeros(nb + 1, dtype=torch.int32)
+    bucket = flat + 1
+    valid = (bucket >= 0) & (bucket < nb)
+    counts = torch.bincount(bucket[valid], minlength=nb)
+    padded = (counts + block_size - 1) // block_size * block_size
+    starts = torch.cumsum(padded, 0) - padded
+    total = int(padded.sum())
+    order = torch.argsort(bucket, stable=True)
+    order = order[valid[order]]
+    pos_in_bucket = torch.arange(order.numel()) - (torch.cumsum(counts, 0) - counts)[bucket[order]]
+    sorted_ids[(starts[bucket[order]] + pos_in_bucket)] = order.to(torch.int32)
+    for b in range(nb):
+        lo, hi = int(starts[b]) // block_size, int(starts[b] + padded[b]) // block_size
+        expert_ids[lo:hi] = b - 1
+    cumsum[:nb] = (starts + counts).to(torch.int32)
+    cumsum[nb] = total
+    return sorted_ids, expert_ids, torch.tensor([total], dtype=torch.int32), cumsum
+
+
+# ----------------------------------------------------------------------------- MoE
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    return F.silu(x[..., :d]) * x[..., d:]
+
+
+def fused_experts_fp8(
+    a: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    w1_s: torch.Tensor,
+    w2_s: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    block_shape: Sequence[int] = (128, 128),
+    compute_dtype: torch.dtype = torch.float32,
+    routed_scaling_factor: Optional[float] = None,
+    no_combine: bool = False,
+    apply_router_weight_on_input: bool = False,
+) -> torch.Tensor:
+    """Block-FP8 W8A8 MoE: for every (token, slot) pair run expert ``ids[t, j]``'s
+    gate_up GEMM -> SiLU*mul -> re-quant -> down GEMM, weight and sum over slots.
+
+    ``compute_dtype`` is the dtype activations are carried in between the
+    kernels (fp32 = the "computed in fp32" oracle)."""
+    T, D = a.shape
+    topk = topk_ids.shape[1]
+    E = w1.shape[0]
+    bk = block_shape[1]
+    a = a.to(compute_dtype)
+    if apply_router_weight_on_input:
+        assert topk == 1
+        a = a * topk_weights.to(compute_dtype)
+    a_rep = a.view(T, 1, D).repeat(1, topk, 1).reshape(-1, D)
+    out = torch.zeros(T * topk, w2.shape[1], dtype=compute_dtype)
+    ids = topk_ids.reshape(-1)
+    a_q, a_s = per_token_group_quant_fp8(a_rep.contiguous(), bk)
+    a_q = a_q.to(torch.float32)
+    for e in range(E):
+        mask = ids == e
+        if mask.sum():
+            inter = w8a8_block_fp8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, output_dtype=compute_dtype)
+            act = silu_and_mul(inter)
+            act_q, act_s = per_token_group_quant_fp8(act.contiguous(), bk)
+            out[mask] = w8a8_block_fp8_matmul(act_q, w2[e], act_s, w2_s[e], block_shape, output_dtype=compute_dtype)
+    out = out.view(T, topk, -1)
+    if not apply_router_weight_on_input:
+        out = out * topk_weights.view(T, topk, 1).to(out.dtype)
+    if no_combine:
+        return out
+    out = out.sum(dim=1)
+    if routed_scaling_factor is not None:
+        out = out * routed_scaling_factor
+    return out
+
+
+# ------------------------------------------------------------------------- routing
+def softmax_topk(logits: torch.Tensor, topk: int, renormalize: bool = True):
+    w = logits.float().softmax(dim=-1)
+    w, ids = torch.topk(w, topk, dim=-1)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids.to(torch.int32)
+
+
+def biased_grouped_topk(
+    logits: torch.Tensor,
+    correction_bias: torch.Tensor,
+    topk: int,
+    num_expert_group: int,
+    topk_group: int,
+    renormalize: bool = True,
+    routed_scaling_factor: Optional[float] = None,
+):
+    """Sigmoid scores; group score = sum of the top-2 biased scores of the group;
+    keep ``topk_group`` groups; top-k experts among them; weights are the unbiased
+    scores, renormalised."""
+    scores = logits.float().sigmoid()
+    T, E = scores.shape
+    sfc = scores + correction_bias.float().unsqueeze(0)
+    group_scores = sfc.view(T, num_expert_group, -1).topk(2, dim=-1)[0].sum(dim=-1)
+    group_idx = torch.topk(group_scores, k=topk_group, dim=-1, sorted=False)[1]
+    group_mask = torch.zeros_like(group_scores)
+    group_mask.scatter_(1, group_idx, 1)
+    score_mask = group_mask.unsqueeze(-1).expand(T, num_expert_group, E // num_expert_group).reshape(T, -1)
+    tmp = sfc.masked_fill(~score_mask.bool(), float("-inf"))
+    ids = torch.topk(tmp, k=topk, dim=-1, sorted=False)[1]
+    w = scores.gather(1, ids)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    if routed_scaling_factor is not None:
+        w = w * routed_scaling_factor
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
+def ep_local_expert_ids(topk_ids: torch.Tensor, num_experts: int, ep_size: int, ep_rank: int):
+    """Expert-parallel id remap: rank ``r`` owns experts ``[r*E/p, (r+1)*E/p)``; local ids are
+    rebased to 0, everything else becomes -1
+    (python/sglang/srt/layers/moe/token_dispatcher/standard.py:172-210)."""
+    per = num_experts // ep_size
+    lo = ep_rank * per
+    local = topk_ids - lo
+    return torch.where((topk_ids >= lo) & (topk_ids < lo + per), local, torch.full_like(topk_ids, -1))
+
+
+def rel_frobenius(x: torch.Tensor, ref: torch.Tensor) -> float:
+    x = x.to(torch.float64)
+    ref = ref.to(torch.float64)
+    return float((x - ref).norm() / ref.norm().clamp(min=1e-30))
