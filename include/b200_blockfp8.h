@@ -1,0 +1,126 @@
+/*
+ * b200_blockfp8 -- C ABI of the B200 (sm_100a) block-FP8 W8A8 linear + fused-MoE kernels.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer owned by the caller unless stated otherwise; the
+ *    library borrows it for the duration of the call, allocates nothing, never
+ *    synchronises and never creates a stream. Work is enqueued on `stream` (a
+ *    cudaStream_t passed as void*).
+ *  - Every entry point returns 0 on success or a negative B200_E_* code; nothing throws.
+ *    b200_status_string() turns a code into text, b200_last_error_detail() gives the
+ *    detail of the most recent failure on the calling thread.
+ *  - dtype codes: B200_BF16 / B200_F16 / B200_F32 for floating tensors,
+ *    B200_I32 / B200_I64 for index tensors.
+ *
+ * The reference has no C ABI for this path (its kernels are torch C++ ops); each entry
+ * point cites the reference operator it replaces, by path inside the reference project.
+ */
+#ifndef B200_BLOCKFP8_H_
+#define B200_BLOCKFP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200_OK = 0,
+  B200_E_BAD_ARG = -1,       /* null pointer, negative size, unknown dtype / mode */
+  B200_E_UNSUPPORTED = -2,   /* legal in the reference but not built here (stated per call) */
+  B200_E_LAUNCH = -3,        /* CUDA reported an error at launch / descriptor encode */
+  B200_E_WORKSPACE = -4,     /* workspace missing or smaller than *_workspace_bytes() */
+  B200_E_TIMEOUT = -5        /* a bounded device-side wait ran out (see b200_read_device_status) */
+};
+
+enum { B200_BF16 = 0, B200_F16 = 1, B200_F32 = 2, B200_I32 = 3, B200_I64 = 4 };
+
+/* quant arithmetic variants (all: amax = max(|x|, eps) over the group, fp32)
+ *   0: s = amax / 448,     q = x / s        (reference torch-native + CUDA v1)
+ *   1: s = amax / 448,     q = x * (1 / s)  (reference Triton row-major)
+ *   2: s = amax * (1/448), q = x * (448 / amax)  (reference CUDA v2)                    */
+enum { B200_QUANT_DIV = 0, B200_QUANT_RECIP = 1, B200_QUANT_V2 = 2 };
+
+const char* b200_status_string(int status);
+const char* b200_last_error_detail(void);
+int b200_abi_version(void);
+
+/* Device-side status word. Kernels with bounded waits (the TMA / tcgen05 pipelines)
+ * record a non-zero code there instead of trapping or spinning for ever.
+ * b200_read_device_status synchronises `stream`, copies the word of the current device
+ * to *out (host pointer) and clears it. 0 = no kernel reported a problem. */
+int b200_read_device_status(int* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * per_token_group_quant_fp8
+ * replaces: python/sglang/srt/layers/quantization/fp8_kernel.py:498-565
+ *           (torch.ops.sgl_kernel.sgl_per_token_group_quant_8bit[_v2],
+ *            sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217)
+ * x [M,K] contiguous (x_dtype bf16/f16/f32) -> q [M,K] FP8 E4M3 bytes, and one fp32 scale per
+ * (row, group) stored at s[m*s_stride_m + g*s_stride_g] (row-major: (K/group,1);
+ * column-major: (1,M); "TMA-aligned": (1, ceil4(M))). group in {16,32,64,128,256,512},
+ * K % group == 0. q rows are 16-byte aligned when K % 16 == 0 (required).            */
+int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s,
+                                   int64_t M, int64_t K, int group,
+                                   int64_t s_stride_m, int64_t s_stride_g,
+                                   float eps, int formula, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * w8a8_block_fp8_matmul
+ * replaces: python/sglang/srt/layers/quantization/fp8_kernel.py:1285-1300 (Triton kernel
+ *           :780-869) and torch.ops.sgl_kernel.fp8_blockwise_scaled_mm
+ *           (sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:425-522)
+ * C[m,n] = sum_kb (sum_{k in kb} A[m,k]*B[n,k]) * As[m,kb] * Bs[n/128,kb], block = [128,128].
+ * A [M,K] e4m3 row-major, B [N,K] e4m3 row-major, As fp32 at As[m*as_stride_m+kb*as_stride_k],
+ * Bs fp32 [ceil(N/128), ceil(K/128)] row-major, C [M,N] (c_dtype bf16/f16/f32) row-major.
+ * Requirements: K % 16 == 0, N % 8 == 0, A, B and C 16-byte aligned.
+ * workspace: b200_w8a8_block_fp8_gemm_workspace_bytes(M,N,K) bytes (may be 0 -> NULL ok). */
+size_t b200_w8a8_block_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m,
+                             int64_t as_stride_k, const void* B, const float* Bs, void* C,
+                             int c_dtype, int64_t M, int64_t N, int64_t K, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * moe_align_block_size
+ * replaces: torch.ops.sgl_kernel.moe_align_block_size
+ *           (sgl-kernel/csrc/moe/moe_align_kernel.cu:317-383; wrapper
+ *            python/sglang/srt/layers/moe/moe_runner/triton_utils/moe_align_block_size.py:19-87)
+ * topk_ids: numel ids (ids_dtype i32/i64) in [-1, num_buckets-1); bucket b holds id b-1.
+ * Outputs: sorted_token_ids int32 [max_pad] (flat indices, ascending inside a bucket, `numel`
+ * in pad slots; slots >= num_post_pad are written only if pad_sorted != 0),
+ * expert_ids int32 [max_blocks] (bucket-1 per block, -1 past the last block),
+ * num_post_pad int32 [1], cumsum int32 [num_buckets+1] (end of each bucket's real entries;
+ * last = padded total). workspace: b200_moe_align_workspace_bytes(numel, num_buckets).     */
+size_t b200_moe_align_workspace_bytes(int64_t numel, int num_buckets);
+int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel,
+                              int num_buckets, int block_size, int32_t* sorted_token_ids,
+                              int64_t max_pad, int32_t* expert_ids, int64_t max_blocks,
+                              int32_t* num_post_pad, int32_t* cumsum, int pad_sorted,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * fused_experts(use_fp8_w8a8=True, block_shape=[128,128])
+ * replaces: python/sglang/srt/layers/moe/moe_runner/triton_utils/fused_moe.py:218-306
+ *           (kernel sequence :401-785: align -> quant -> grouped GEMM -> silu_and_mul ->
+ *            quant -> grouped GEMM * topk_weight -> sum over top-k)
+ * hidden [T,H] (h_dtype bf16/f16), w1 [E,2I,H] e4m3 (gate rows [0,I), up rows [I,2I)),
+ * w2 [E,H,I] e4m3, w1_scale fp32 [E,2I/128,H/128], w2_scale fp32 [E,H/128,I/128],
+ * topk_weights fp32 [T,topk], topk_ids int32 [T,topk] with values in [-1,E) (-1 = expert
+ * not on this rank: contributes 0). out [T,H] (or [T,topk,H] when no_combine != 0), h_dtype;
+ * out may alias hidden (the reference's inplace=True). H % 128 == 0, I % 128 == 0.
+ * routed_scaling_factor multiplies the combined output (pass 1.0f for none).
+ * workspace: b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I) bytes, 256-B aligned. */
+size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, int E, int64_t H, int64_t I);
+int b200_fused_experts_fp8(const void* hidden, int h_dtype, const void* w1, const void* w2,
+                           const float* w1_scale, const float* w2_scale,
+                           const float* topk_weights, const int32_t* topk_ids, void* out,
+                           int64_t T, int topk, int E, int64_t H, int64_t I, int no_combine,
+                           int apply_router_weight_on_input, float routed_scaling_factor,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_BLOCKFP8_H_ */

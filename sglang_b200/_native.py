@@ -1,0 +1,119 @@
+"""ctypes binding of the C ABI declared in ``include/b200_blockfp8.h``.
+
+The shared library is the only implementation: if it is missing it is built in-tree with
+nvcc, and if that fails the import error propagates. There is no CPU or torch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "_lib", "libb200_blockfp8.so")
+
+# Every symbol the header declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "b200_status_string": (c_char_p, [c_int]),
+    "b200_last_error_detail": (c_char_p, []),
+    "b200_abi_version": (c_int, []),
+    "b200_read_device_status": (c_int, [POINTER(c_int), c_void_p]),
+    "b200_per_token_group_quant_fp8": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int64, c_float, c_int, c_void_p],
+    ),
+    "b200_w8a8_block_fp8_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "b200_w8a8_block_fp8_gemm": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
+         c_void_p, c_size_t, c_void_p],
+    ),
+    "b200_moe_align_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "b200_moe_align_block_size": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int,
+         c_void_p, c_size_t, c_void_p],
+    ),
+    "b200_fused_experts_fp8_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int64, c_int64]),
+    "b200_fused_experts_fp8": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+         c_int, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_size_t, c_void_p],
+    ),
+}
+
+BF16, F16, F32, I32, I64 = 0, 1, 2, 3, 4
+DTYPE_CODE = {
+    torch.bfloat16: BF16,
+    torch.float16: F16,
+    torch.float32: F32,
+    torch.int32: I32,
+    torch.int64: I64,
+}
+
+E_BAD_ARG, E_UNSUPPORTED, E_LAUNCH, E_WORKSPACE, E_TIMEOUT = -1, -2, -3, -4, -5
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load (building first if needed) the native library and bind every declared symbol."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            from . import build as _build
+
+            _build.build()
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    """Map a C-ABI status to the reference's exception types: precondition failures raise
+    AssertionError (the reference asserts in Python), everything else RuntimeError."""
+    if status == 0:
+        return
+    lib = load()
+    msg = f"{what}: {lib.b200_status_string(status).decode()}: {lib.b200_last_error_detail().decode()}"
+    if status == E_BAD_ARG:
+        raise AssertionError(msg)
+    if status == E_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise RuntimeError(msg)
+
+
+def require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "sglang_b200 operators run on CUDA (sm_100a) tensors only; got a tensor on "
+                f"{t.device}. There is no CPU path."
+            )
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def current_stream(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def read_device_status() -> int:
+    """Synchronise the current stream and return (and clear) the device status word."""
+    out = c_int(0)
+    check(load().b200_read_device_status(ctypes.byref(out), current_stream()), "read_device_status")
+    return out.value

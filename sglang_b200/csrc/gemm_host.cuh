@@ -1,0 +1,118 @@
+// Host side of the block-FP8 GEMM: TMA descriptor encoding and the launch helper shared by
+// the dense linear entry point and the fused-MoE entry point.
+#pragma once
+
+#include "gemm_kernel.cuh"
+
+namespace b200 {
+
+// cuTensorMapEncodeTiled, resolved through the runtime so the library needs no -lcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major [rows, k_bytes] byte matrix, box = [box_rows x 128 bytes], 128-byte swizzle,
+// out-of-range elements read as zero.
+inline int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t k_bytes, uint32_t box_rows,
+                        const char* what) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    set_error_detail("cuTensorMapEncodeTiled is not available from the driver");
+    return B200_E_LAUNCH;
+  }
+  cuuint64_t dims[2] = {k_bytes, rows};
+  cuuint64_t strides[1] = {k_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error_detail("cuTensorMapEncodeTiled(%s: rows=%llu k=%llu box_rows=%u) failed with CUresult %d", what,
+                     (unsigned long long)rows, (unsigned long long)k_bytes, box_rows, (int)r);
+    return B200_E_LAUNCH;
+  }
+  return B200_OK;
+}
+
+inline int sm_count() {
+  static thread_local int dev_cached = -1, sms = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != dev_cached) {
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    dev_cached = dev;
+  }
+  return sms > 0 ? sms : 148;
+}
+
+template <int BN, int MODE, typename OutT>
+inline int launch_gemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                            cudaStream_t st) {
+  auto k = block_fp8_gemm_kernel<BN, MODE, OutT>;
+  // per device and cheap: set on every launch rather than caching per device
+  const size_t smem = GemmCfg<BN>::smem_bytes(MODE);
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error_detail("cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
+    return B200_E_LAUNCH;
+  }
+  k<<<grid, GemmCfg<BN>::kThreads, smem, st>>>(ta, tb, p);
+  return check_launch("block_fp8_gemm_kernel");
+}
+
+// a_rows x K (fp8) times b_rows_total x K (fp8; grouped: experts stacked) -> C.
+// p must be filled except num_kb / n_blocks / n_tiles / m_tiles / group_m / status.
+// m_tiles_hint: expected number of live 128-row tiles when that is decided on the device.
+template <int MODE, typename OutT>
+inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmParams p, int force_bn,
+                       cudaStream_t st, int64_t m_tiles_hint = 0) {
+  p.num_kb = (int)cdiv(p.K, kBK);
+  p.n_blocks = (int)cdiv(p.N, 128);
+  p.m_tiles = (int)cdiv(p.M, kBM);
+  p.status = device_status_word();
+  if (!p.status) {
+    set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
+  const int sms = sm_count();
+  // 128 x 256 tiles halve the shared-memory traffic per flop; fall back to 128 x 128 when
+  // that would leave SMs idle (small problems) or N has no second 128-block.
+  int bn = 256;
+  if (MODE == GEMM_GROUPED_SILU_QUANT) force_bn = 256;  // gate + up halves of one tile
+  const int64_t m_tiles_live = m_tiles_hint > 0 ? m_tiles_hint : p.m_tiles;  // grouped: expected live row tiles
+  if (p.N <= 128 || m_tiles_live * cdiv(p.N, 256) < sms) bn = 128;
+  if (force_bn == 128 || force_bn == 256) bn = force_bn;
+  p.n_tiles = MODE == GEMM_GROUPED_SILU_QUANT ? p.N / 128 : (int)cdiv(p.N, bn);
+  p.group_m = 16;
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  if (tiles == 0) return B200_OK;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  CUtensorMap ta, tb;
+  int rc = make_tmap_u8(&ta, A, (uint64_t)p.M, (uint64_t)p.K, kBM, "A");
+  if (rc) return rc;
+  rc = make_tmap_u8(&tb, B, (uint64_t)b_rows_total, (uint64_t)p.K,
+                    MODE == GEMM_GROUPED_SILU_QUANT ? 128u : (uint32_t)bn, "B");
+  if (rc) return rc;
+  if (bn == 256) return launch_gemm_inst<256, MODE, OutT>(ta, tb, p, grid, st);
+  if constexpr (MODE == GEMM_GROUPED_SILU_QUANT) {
+    set_error_detail("gate_up GEMM needs 256-wide tiles");
+    return B200_E_BAD_ARG;
+  } else {
+    return launch_gemm_inst<128, MODE, OutT>(ta, tb, p, grid, st);
+  }
+}
+
+}  // namespace b200

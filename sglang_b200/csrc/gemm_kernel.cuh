@@ -1,0 +1,382 @@
+// Block-FP8 GEMM for sm_100a: C[m,n] = sum_kb (A_kb . B_kb^T)[m,n] * As[m,kb] * Bs[n/128,kb].
+//
+// One persistent CTA per SM walks output tiles of 128 x BN (BN = 128 or 256). Roles:
+//   warps [0, BN/32)  "promotion" warps: per K block they pull the fp32 partial product out
+//                     of TMEM (tcgen05.ld), multiply by the two block scales and accumulate
+//                     in registers (128 accumulators per thread); at the end of a tile they
+//                     convert and store the row they own.
+//   warp  BN/32       TMA producer: cp.async.bulk.tensor (128-byte swizzle, no multicast)
+//                     of the A [128 x 128 B] and B [BN x 128 B] tiles into an S-stage ring.
+//   warp  BN/32 + 1   MMA issuer: 4 x tcgen05.mma (K = 32 each) per K block into one of two
+//                     TMEM accumulator buffers, tcgen05.commit to free the smem stage and to
+//                     hand the buffer to the promotion warps.
+// Because fp32 block scales change every 128 of K, the tensor core never accumulates
+// across K blocks: TMEM is a double-buffered staging area and the running sum lives in
+// registers, so the MMA of block k+1 overlaps the promotion of block k.
+//
+// The same kernel serves the dense linear (MODE 0) and the two grouped MoE GEMMs, whose
+// A rows are laid out in expert-sorted, 128-row-padded order:
+//   MODE 1 (gate_up): the B tile is 128 gate rows + the matching 128 up rows of the expert,
+//           and the tile epilogue computes silu(gate)*up in fp32 and re-quantises it to FP8
+//           with its 1x128 scale straight from the accumulators (no 16-bit round trip);
+//   MODE 2 (down): rows are scattered to their (token, slot) position, times the router weight.
+#pragma once
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+enum { GEMM_DENSE = 0, GEMM_GROUPED_SILU_QUANT = 1, GEMM_GROUPED_SCATTER = 2 };
+
+struct GemmParams {
+  const float* As;  // A scales: As[m*as_sm + kb*as_sk]
+  int64_t as_sm, as_sk;
+  const float* Bs;  // [experts][n_blocks][num_kb]
+  void* C;
+  int64_t ldc;     // elements
+  int M, N, K;     // M = rows of A (grouped: capacity of the sorted layout)
+  int num_kb;      // ceil(K/128)
+  int n_blocks;    // ceil(N/128): rows of Bs per expert
+  int n_tiles;     // ceil(N/BN)
+  int m_tiles;     // ceil(M/128) (grouped: upper bound; the live count is read on device)
+  int group_m;     // tiles of M swept together for L2 reuse
+  // grouped modes
+  const int32_t* expert_ids;    // [m_tiles] expert of every 128-row block, -1 = skip
+  const int32_t* num_post_pad;  // [1] live rows (multiple of 128)
+  const int32_t* sorted_ids;    // [M] flat (token*topk+slot) index of every row, >= numel = pad
+  const float* topk_weights;    // [numel] (MODE 2; may be null = no weighting)
+  int numel;
+  // MODE 1 outputs: FP8 activation [M, N] (N = intermediate size I; B holds 2I rows per
+  // expert) and its scales, column-major: q_scales[(n/128)*q_scale_ld + row]
+  uint8_t* q_out;
+  float* q_scales;
+  int64_t q_scale_ld;
+  int* status;  // device status word
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;  // bytes == elements (fp8) == one scale block == one swizzle row
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kEpiWarps = BN / 32;  // 4 or 8: warp e -> TMEM lanes 32*(e%4), columns 128*(e/4)
+  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  static constexpr int kStageA = kBM * kBK;
+  static constexpr int kStageB = BN * kBK;
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
+  static constexpr int kExchangeBytes = 64 * kBM * 4;  // MODE 1: 64 columns x 128 rows of fp32
+  static constexpr size_t smem_bytes(int mode) {
+    return (size_t)kStages * (kStageA + kStageB) + (mode == 1 ? kExchangeBytes : 0) + 1024 /*align slack*/ +
+           256 /*barriers*/;
+  }
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// silu(g) * u with the fast exponential / reciprocal (relative error ~1e-6: far below the
+// FP8 quantisation step that follows).
+__device__ __forceinline__ float silu_mul_fast(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const float* a);
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float* a) {
+  uint4 v;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn(a[0], a[1]); v.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(a[2], a[3]); v.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(a[4], a[5]); v.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(a[6], a[7]); v.w = *reinterpret_cast<uint32_t*>(&t);
+  *reinterpret_cast<uint4*>(dst) = v;
+}
+template <>
+__device__ __forceinline__ void store8<__half>(__half* dst, const float* a) {
+  uint4 v;
+  __half2 t;
+  t = __floats2half2_rn(a[0], a[1]); v.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(a[2], a[3]); v.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(a[4], a[5]); v.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(a[6], a[7]); v.w = *reinterpret_cast<uint32_t*>(&t);
+  *reinterpret_cast<uint4*>(dst) = v;
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float* a) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a[0], a[1], a[2], a[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
+}
+
+// tile index -> (m_tile, n_tile): sweep group_m row-tiles for every column tile before moving
+// on, so the CTAs running together share A rows and B columns in L2.
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
+  const int per_group = group_m * n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * group_m;
+  const int rows = min(group_m, m_tiles - first_m);
+  const int r = t - g * per_group;
+  mt = first_m + r % rows;
+  nt = r / rows;
+}
+
+template <int BN, int MODE, typename OutT>
+__global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
+block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t sA = smem_base;
+  const uint32_t sB = smem_base + S * Cfg::kStageA;
+  float* exchange = reinterpret_cast<float*>(smem_al + (size_t)S * (Cfg::kStageA + Cfg::kStageB));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + (size_t)S * (Cfg::kStageA + Cfg::kStageB) +
+                                               (MODE == GEMM_GROUPED_SILU_QUANT ? Cfg::kExchangeBytes : 0));
+  const uint32_t bar0 = ptx::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 5);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kProducerWarp = Cfg::kEpiWarps, kMmaWarp = Cfg::kEpiWarps + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar(b), 1);
+      ptx::mbar_init(tempty_bar(b), Cfg::kEpiWarps);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // live problem size (grouped: decided on the device by the align kernel)
+  int m_tiles = p.m_tiles;
+  if (MODE != GEMM_DENSE) m_tiles = min(m_tiles, *p.num_post_pad / kBM);
+  const int total_tiles = m_tiles * p.n_tiles;
+  const int num_kb = p.num_kb;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
+      int b_row = nt * BN, b_row2 = 0;
+      if (MODE != GEMM_DENSE) {
+        const int e = p.expert_ids[mt];
+        if (e < 0) continue;
+        if (MODE == GEMM_GROUPED_SILU_QUANT) {
+          b_row = e * 2 * p.N + nt * 128;  // gate rows
+          b_row2 = b_row + p.N;            // matching up rows
+        } else {
+          b_row += e * p.N;
+        }
+      }
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % S;
+        ok = ptx::mbar_wait(empty_bar(s), ((it / S) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          ptx::mbar_expect_tx(full_bar(s), Cfg::kStageA + Cfg::kStageB);
+          ptx::tma_load_2d(sA + s * Cfg::kStageA, &tmap_a, kb * kBK, mt * kBM, full_bar(s));
+          ptx::tma_load_2d(sB + s * Cfg::kStageB, &tmap_b, kb * kBK, b_row, full_bar(s));
+          if (MODE == GEMM_GROUPED_SILU_QUANT)  // B box is 128 rows in this mode: second half of the stage
+            ptx::tma_load_2d(sB + s * Cfg::kStageB + 128 * kBK, &tmap_b, kb * kBK, b_row2, full_bar(s));
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = ptx::idesc_e4m3_f32(kBM, BN);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
+      if (MODE != GEMM_DENSE && p.expert_ids[mt] < 0) continue;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % S, b = it & 1;
+        ok = ptx::mbar_wait(tempty_bar(b), ((it >> 1) & 1) ^ 1, abort_flag) &&
+             ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint64_t da = ptx::smem_desc_sw128(sA + s * Cfg::kStageA);
+          const uint64_t db = ptx::smem_desc_sw128(sB + s * Cfg::kStageB);
+          const uint32_t d = tmem_base + b * BN;
+#pragma unroll
+          for (int k = 0; k < kBK / 32; ++k)  // +32 bytes along K inside the swizzle row = +2 in the address field
+            ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, k > 0);
+          ptx::mma_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
+          ptx::mma_commit(tfull_bar(b));   // partial product ready for the promotion warps
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- promotion warps
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
+      int expert = 0;
+      if (MODE != GEMM_DENSE) {
+        expert = p.expert_ids[mt];
+        if (expert < 0) continue;
+      }
+      const int row = mt * kBM + row_in_tile;
+      const int col0 = MODE == GEMM_GROUPED_SILU_QUANT ? nt * 128 : nt * BN + half * 128;
+      const bool row_ok = row < p.M;
+      const float* as_ptr = p.As + (int64_t)(row_ok ? row : 0) * p.as_sm;
+      // row of Bs: 128-row block of B this thread's columns come from (MODE 1: gate block nt
+      // for the first 128 TMEM columns, up block I/128 + nt for the other 128)
+      const int nb = MODE == GEMM_GROUPED_SILU_QUANT ? half * p.n_blocks + nt : min(col0 / 128, p.n_blocks - 1);
+      const int bs_rows = MODE == GEMM_GROUPED_SILU_QUANT ? 2 * p.n_blocks : p.n_blocks;
+      const float* bs_ptr = p.Bs + ((int64_t)expert * bs_rows + nb) * num_kb;
+
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      float sc_next = row_ok ? __ldg(as_ptr) * __ldg(bs_ptr) : 0.f;
+
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int b = it & 1;
+        const float sc = sc_next;
+        if (kb + 1 < num_kb) sc_next = row_ok ? __ldg(as_ptr + (int64_t)(kb + 1) * p.as_sk) * __ldg(bs_ptr + kb + 1) : 0.f;
+        ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t ta = lane_base + b * BN;
+        uint32_t va[32], vb[32];
+        ptx::tmem_ld32(ta, va);
+        ptx::tmem_ld_wait(va);
+        ptx::tmem_ld32(ta + 32, vb);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(va[j]), sc, acc[j]);
+        ptx::tmem_ld_wait(vb);
+        ptx::tmem_ld32(ta + 64, va);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(vb[j]), sc, acc[32 + j]);
+        ptx::tmem_ld_wait(va);
+        ptx::tmem_ld32(ta + 96, vb);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(__uint_as_float(va[j]), sc, acc[64 + j]);
+        ptx::tmem_ld_wait(vb);
+        // every TMEM read of this buffer has landed: give it back to the MMA warp
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(__uint_as_float(vb[j]), sc, acc[96 + j]);
+      }
+      if (!ok) break;
+
+      // ------------------------------------------------------------ tile epilogue
+      if (MODE == GEMM_GROUPED_SILU_QUANT) {
+        // warps 4-7 hold `up`, warps 0-3 hold `gate` of the same rows and columns: hand `up`
+        // over through shared memory 64 columns at a time ([column][row]: conflict free).
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          if (half == 1) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) exchange[j * kBM + row_in_tile] = acc[64 * r + j];
+          }
+          named_bar_sync(1, Cfg::kEpiWarps * 32);
+          if (half == 0) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              acc[64 * r + j] = silu_mul_fast(acc[64 * r + j], exchange[j * kBM + row_in_tile]);
+          }
+          named_bar_sync(1, Cfg::kEpiWarps * 32);
+        }
+        if (half == 0 && row_ok) {
+          // this thread's 128 columns are exactly one 1x128 quantisation group
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 128; ++j) amax = fmaxf(amax, fabsf(acc[j]));
+          amax = fmaxf(amax, 1e-10f);
+          const float inv = __fdividef(448.0f, amax);
+          uint8_t* dst = p.q_out + (int64_t)row * p.N + col0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float q[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) q[i] = fminf(fmaxf(acc[16 * j + i] * inv, -448.f), 448.f);
+            uint4 v;
+            v.x = pack4_e4m3(q[0], q[1], q[2], q[3]);
+            v.y = pack4_e4m3(q[4], q[5], q[6], q[7]);
+            v.z = pack4_e4m3(q[8], q[9], q[10], q[11]);
+            v.w = pack4_e4m3(q[12], q[13], q[14], q[15]);
+            *reinterpret_cast<uint4*>(dst + 16 * j) = v;
+          }
+          p.q_scales[(int64_t)nt * p.q_scale_ld + row] = __fdiv_rn(amax, 448.0f);
+        }
+        continue;
+      }
+      int64_t out_row = row;
+      bool store = row_ok;
+      if (MODE == GEMM_GROUPED_SCATTER) {
+        const int flat = store ? p.sorted_ids[row] : p.numel;
+        store = store && flat < p.numel;
+        out_row = flat;
+        if (store && p.topk_weights != nullptr) {
+          const float w = __ldg(p.topk_weights + flat);
+#pragma unroll
+          for (int j = 0; j < 128; ++j) acc[j] *= w;
+        }
+      }
+      if (store) {
+        OutT* dst = static_cast<OutT*>(p.C) + out_row * p.ldc + col0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, acc + j * 8);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // A wait ran out: give copies / MMAs still in flight time to land before TMEM is freed.
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, 0, 1);  // the host reads this word
+  if (warp == kMmaWarp) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,216 @@
+// fused_experts(use_fp8_w8a8=True, block_shape=[128,128]) for sm_100a.
+//
+// Launch sequence (all on the caller's stream, no host sync):
+//   1 align            token->expert buckets padded to 128 rows                 (align.cu)
+//   2 gather_quant     hidden rows -> expert-sorted FP8 rows + 1x128 scales     (HBM bound)
+//   3 grouped GEMM 1   sorted rows x w1[expert]^T; the epilogue applies silu(gate)*up in fp32
+//                      and re-quantises to FP8 + 1x128 scales from the accumulators (tcgen05)
+//   4 grouped GEMM 2   x w2[expert]^T, * router weight, scattered to (token, slot)
+//   5 sum_reduce       fp32 sum over the top-k slots -> out                     (HBM bound)
+// Scales of the two intermediate activations are stored column-major ([K/128][rows]) so a
+// GEMM promotion warp reads 32 consecutive floats per K block.
+#include <stdlib.h>
+
+#include "gemm_host.cuh"
+
+namespace b200 {
+
+constexpr int kMoeBlockM = 128;
+
+// One thread = 16 consecutive elements of one sorted row (8 lanes share a 128-group).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_quant_kernel(
+    const T* __restrict__ hidden, const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
+    const int32_t* __restrict__ num_post_pad, const float* __restrict__ in_weights, uint8_t* __restrict__ q,
+    float* __restrict__ s, int64_t total_chunks, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t slot = c / chunks_per_row;
+  const int chunk = (int)(c - slot * chunks_per_row);
+  bool active = c < total_chunks && slot < *num_post_pad;
+  if (active) active = expert_ids[slot / kMoeBlockM] >= 0;
+  int flat = numel;
+  if (active) flat = sorted_ids[slot];
+  const bool real = active && flat < numel;
+  float f[16];
+  if (real) {
+    Vec16<T>::load(hidden + (int64_t)(flat / topk) * H + chunk * 16, f);
+    if (in_weights != nullptr) {
+      const float w = __ldg(in_weights + flat);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = to_f32<T>(from_f32<T>(f[i] * w));  // reference rounds to the input dtype
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = 0.f;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+  amax = fmaxf(group_max<8>(amax), 1e-10f);
+  uint4 out;
+  const float scale = quant16(f, amax, B200_QUANT_DIV, out);
+  if (active) {  // pad rows of live blocks are written as zeros so the GEMM reads defined bytes
+    *reinterpret_cast<uint4*>(q + slot * H + chunk * 16) = out;
+    if ((threadIdx.x & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot] = scale;
+  }
+}
+
+// out[t, :] = scale * sum_j y[t*topk + j, :] over the slots whose expert id is valid.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_sum_reduce_kernel(const T* __restrict__ y, const int32_t* __restrict__ topk_ids,
+                                                             T* __restrict__ out, int64_t T_tokens, int topk, int E,
+                                                             int64_t H, float scale) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vec_per_row = (int)(H / 8);
+  if (c >= T_tokens * vec_per_row) return;
+  const int64_t t = c / vec_per_row;
+  const int v = (int)(c - t * vec_per_row);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int j = 0; j < topk; ++j) {
+    const int e = topk_ids[t * topk + j];
+    if (e < 0 || e >= E) continue;
+    const uint4 r = ld_nc_16(y + (t * topk + j) * H + v * 8);
+    const T* h = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+  }
+  uint4 o;
+  T* oh = reinterpret_cast<T*>(&o);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * scale);
+  *reinterpret_cast<uint4*>(out + t * H + v * 8) = o;
+}
+
+struct MoeWorkspace {
+  int64_t cap;  // rows of the expert-sorted layout (multiple of 128)
+  int64_t cap_blocks;
+  size_t off_sorted, off_expert, off_npp, off_cumsum, off_align, off_aq1, off_as1, off_aq2, off_as2, off_c3, total;
+};
+
+static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, int64_t I) {
+  MoeWorkspace w = {};
+  const int64_t numel = T * topk;
+  int64_t max_pad = numel < E + 1 ? numel * kMoeBlockM : numel + (int64_t)(E + 1) * (kMoeBlockM - 1);
+  w.cap = cdiv(max_pad, kMoeBlockM) * kMoeBlockM;
+  w.cap_blocks = w.cap / kMoeBlockM;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { size_t at = o; o = align_up(o + bytes, 256); return at; };
+  w.off_sorted = take((size_t)w.cap * 4);
+  w.off_expert = take((size_t)w.cap_blocks * 4);
+  w.off_npp = take(4);
+  w.off_cumsum = take((size_t)(E + 2) * 4);
+  w.off_align = take(b200_moe_align_workspace_bytes(numel, E + 1));
+  w.off_aq1 = take((size_t)w.cap * H);
+  w.off_as1 = take((size_t)w.cap * (H / 128) * 4);
+  w.off_aq2 = take((size_t)w.cap * I);
+  w.off_as2 = take((size_t)w.cap * (I / 128) * 4);
+  w.off_c3 = take((size_t)numel * H * 2);
+  w.total = o;
+  return w;
+}
+
+template <typename T>
+static int run_fused_experts(const void* hidden, const void* w1, const void* w2, const float* w1_scale,
+                             const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
+                             int64_t T_tokens, int topk, int E, int64_t H, int64_t I, int no_combine,
+                             int weight_on_input, float routed_scale, uint8_t* ws, cudaStream_t st) {
+  const MoeWorkspace L = moe_workspace_layout(T_tokens, topk, E, H, I);
+  const int64_t numel = T_tokens * topk;
+  int32_t* sorted = reinterpret_cast<int32_t*>(ws + L.off_sorted);
+  int32_t* expert_ids = reinterpret_cast<int32_t*>(ws + L.off_expert);
+  int32_t* npp = reinterpret_cast<int32_t*>(ws + L.off_npp);
+  int32_t* cumsum = reinterpret_cast<int32_t*>(ws + L.off_cumsum);
+  uint8_t* aq1 = ws + L.off_aq1;
+  float* as1 = reinterpret_cast<float*>(ws + L.off_as1);
+  uint8_t* aq2 = ws + L.off_aq2;
+  float* as2 = reinterpret_cast<float*>(ws + L.off_as2);
+  T* c3 = no_combine ? static_cast<T*>(out) : reinterpret_cast<T*>(ws + L.off_c3);
+
+  int rc = b200_moe_align_block_size(topk_ids, B200_I32, numel, E + 1, kMoeBlockM, sorted, L.cap, expert_ids,
+                                     L.cap_blocks, npp, cumsum, 1, ws + L.off_align,
+                                     b200_moe_align_workspace_bytes(numel, E + 1), st);
+  if (rc) return rc;
+  if (no_combine) {
+    // rows of slots whose expert is not on this rank are never written by GEMM 2
+    cudaError_t e = cudaMemsetAsync(out, 0, (size_t)numel * H * sizeof(T), st);
+    if (e != cudaSuccess) {
+      set_error_detail("memset(out): %s", cudaGetErrorString(e));
+      return B200_E_LAUNCH;
+    }
+  }
+  {
+    const int cpr = (int)(H / 16);
+    const int64_t total = L.cap * cpr;
+    moe_gather_quant_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
+        static_cast<const T*>(hidden), sorted, expert_ids, npp, weight_on_input ? topk_weights : nullptr, aq1, as1,
+        total, cpr, H, (int)numel, topk, L.cap);
+    if ((rc = check_launch("moe_gather_quant"))) return rc;
+  }
+  int force_bn = 0;
+  if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);
+  // expected live row tiles: every pair once, plus up to one partial tile per expert
+  const int64_t tiles_hint = cdiv(numel, kMoeBlockM) + (numel < E ? numel : E) / 2;
+  GemmParams p = {};
+  p.expert_ids = expert_ids; p.num_post_pad = npp; p.sorted_ids = sorted; p.numel = (int)numel;
+  p.M = (int)L.cap;
+  // GEMM 1: [cap, H] x w1[E, 2I, H]^T -> silu(gate)*up -> FP8 [cap, I] + column-major scales
+  p.As = as1; p.as_sm = 1; p.as_sk = L.cap; p.Bs = w1_scale; p.C = nullptr; p.ldc = 0;
+  p.N = (int)I; p.K = (int)H; p.topk_weights = nullptr;
+  p.q_out = aq2; p.q_scales = as2; p.q_scale_ld = L.cap;
+  if ((rc = launch_gemm<GEMM_GROUPED_SILU_QUANT, T>(aq1, w1, (int64_t)E * 2 * I, p, 256, st, tiles_hint))) return rc;
+  // GEMM 2: [cap, I] x w2[E, H, I]^T -> rows scattered to (token, slot), times the router weight
+  p.As = as2; p.as_sk = L.cap; p.Bs = w2_scale; p.C = c3; p.ldc = H; p.N = (int)H; p.K = (int)I;
+  p.topk_weights = weight_on_input ? nullptr : topk_weights;
+  if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, T>(aq2, w2, (int64_t)E * H, p, force_bn, st, tiles_hint))) return rc;
+  if (!no_combine) {
+    const int64_t total = T_tokens * (H / 8);
+    moe_sum_reduce_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(c3, topk_ids, static_cast<T*>(out), T_tokens,
+                                                                        topk, E, H, routed_scale);
+    if ((rc = check_launch("moe_sum_reduce"))) return rc;
+  }
+  return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, int E, int64_t H, int64_t I) {
+  if (T <= 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0) return 0;
+  return b200::moe_workspace_layout(T, topk, E, H, I).total;
+}
+
+extern "C" int b200_fused_experts_fp8(const void* hidden, int h_dtype, const void* w1, const void* w2,
+                                      const float* w1_scale, const float* w2_scale, const float* topk_weights,
+                                      const int32_t* topk_ids, void* out, int64_t T, int topk, int E, int64_t H,
+                                      int64_t I, int no_combine, int apply_router_weight_on_input,
+                                      float routed_scaling_factor, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(T >= 0 && topk > 0 && E > 0 && H > 0 && I > 0, "fused_experts: bad shape");
+  if (T == 0) return B200_OK;
+  B200_CHECK_ARG(hidden && w1 && w2 && w1_scale && w2_scale && topk_weights && topk_ids && out,
+                 "fused_experts: null pointer");
+  B200_UNSUPPORTED(H % 128 != 0 || I % 128 != 0, "fused_experts: H=%lld and I=%lld must be multiples of 128",
+                   (long long)H, (long long)I);
+  B200_UNSUPPORTED(E + 1 > 1025, "fused_experts: more than 1024 experts");
+  B200_UNSUPPORTED(T * topk >= (1LL << 30), "fused_experts: too many (token, slot) pairs");
+  B200_CHECK_ARG(!apply_router_weight_on_input || topk == 1, "apply_router_weight_on_input needs topk == 1");
+  B200_CHECK_ARG(((uintptr_t)hidden & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w1 & 15) == 0 &&
+                     ((uintptr_t)w2 & 15) == 0, "fused_experts: tensors must be 16-byte aligned");
+  const size_t need = b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0) {
+    set_error_detail("fused_experts: workspace %zu < %zu bytes or not 256-byte aligned", workspace_bytes, need);
+    return B200_E_WORKSPACE;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (h_dtype == B200_BF16)
+    return run_fused_experts<__nv_bfloat16>(hidden, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T, topk, E,
+                                            H, I, no_combine, apply_router_weight_on_input, routed_scaling_factor, ws, st);
+  if (h_dtype == B200_F16)
+    return run_fused_experts<__half>(hidden, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T, topk, E, H, I,
+                                     no_combine, apply_router_weight_on_input, routed_scaling_factor, ws, st);
+  set_error_detail("fused_experts: hidden dtype code %d is not bf16/f16", h_dtype);
+  return B200_E_UNSUPPORTED;
+}

@@ -1,0 +1,74 @@
+// Status strings, thread-local error detail and the per-device status word.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+static thread_local char g_detail[512] = "";
+
+void set_error_detail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_detail, sizeof(g_detail), fmt, ap);
+  va_end(ap);
+}
+
+// One word per device that loads the library. Kernels with bounded waits write a non-zero
+// code here (atomicCAS from 0, so the first failure is kept) and return normally.
+__device__ int g_device_status = 0;
+
+int* device_status_word() {
+  // The symbol's device address differs per device; resolve it with that device current.
+  static thread_local int cached_dev = -1;
+  static thread_local int* cached_ptr = nullptr;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (dev != cached_dev) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+    cached_ptr = static_cast<int*>(p);
+    cached_dev = dev;
+  }
+  return cached_ptr;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+const char* b200_status_string(int status) {
+  switch (status) {
+    case B200_OK: return "ok";
+    case B200_E_BAD_ARG: return "bad argument";
+    case B200_E_UNSUPPORTED: return "unsupported configuration";
+    case B200_E_LAUNCH: return "CUDA launch / descriptor error";
+    case B200_E_WORKSPACE: return "workspace missing or too small";
+    case B200_E_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+const char* b200_last_error_detail(void) { return b200::g_detail; }
+
+int b200_abi_version(void) { return 1; }
+
+int b200_read_device_status(int* out, void* stream) {
+  B200_CHECK_ARG(out != nullptr, "out is null");
+  int* word = b200::device_status_word();
+  if (!word) {
+    b200::set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(out, word, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(word, 0, sizeof(int), st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    b200::set_error_detail("read_device_status: %s", cudaGetErrorString(e));
+    return B200_E_LAUNCH;
+  }
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,199 @@
+"""Block-FP8 operators with the reference's names, arguments and error behaviour
+(python/sglang/srt/layers/quantization/fp8_kernel.py and fp8_utils.py), executed by the
+hand-written sm_100a kernels behind the C ABI. CUDA tensors only; no fallback.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+fp8_dtype = torch.float8_e4m3fn
+fp8_max = 448.0
+fp8_min = -448.0
+
+# Which of the reference's three quant arithmetic variants is computed (see the C header):
+# 0 = torch-native / CUDA-v1 formula (default, the parity oracle), 1 = Triton row-major, 2 = CUDA v2.
+_QUANT_FORMULA = 0
+
+
+def set_quant_formula(mode: int) -> None:
+    global _QUANT_FORMULA
+    assert mode in (0, 1, 2), "formula mode must be 0, 1 or 2"
+    _QUANT_FORMULA = mode
+
+
+def ceil_align(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+def create_per_token_group_quant_fp8_output_scale(
+    x_shape,
+    device,
+    group_size: int,
+    column_major_scales: bool,
+    scale_tma_aligned: bool,
+    scale_ue8m0: bool,
+) -> torch.Tensor:
+    """Scale buffer in one of the reference's layouts (fp8_kernel.py:454-495): row-major
+    ``[..., M, K/g]``; column-major (same shape, strides ``(1, M)``); column-major with the
+    M extent of the storage padded to a multiple of 4 ("TMA aligned")."""
+    if scale_ue8m0:
+        raise NotImplementedError("scale_ue8m0 (packed power-of-two scales) is not part of this path")
+    x_shape = tuple(x_shape)
+    if column_major_scales:
+        if scale_tma_aligned:
+            aligned = ceil_align(x_shape[-2], 4)
+            return torch.empty(
+                x_shape[:-2] + (x_shape[-1] // group_size, aligned), device=device, dtype=torch.float32
+            ).transpose(-1, -2)[..., : x_shape[-2], :]
+        return torch.empty(
+            (x_shape[-1] // group_size,) + x_shape[:-1], device=device, dtype=torch.float32
+        ).permute(-1, -2)
+    return torch.empty(x_shape[:-1] + (x_shape[-1] // group_size,), device=device, dtype=torch.float32)
+
+
+def per_token_group_quant_fp8(
+    x: torch.Tensor,
+    group_size: int,
+    eps: float = 1e-10,
+    column_major_scales: bool = False,
+    scale_tma_aligned: bool = False,
+    scale_ue8m0: bool = False,
+    fuse_silu_and_mul: bool = False,
+    masked_m: Optional[torch.Tensor] = None,
+    enable_v2: Optional[bool] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row, per-``group_size`` FP8 E4M3 quantisation; returns ``(x_q, x_s)``.
+
+    Same contract as the reference's ``per_token_group_quant_fp8``
+    (fp8_kernel.py:498-565): ``x`` contiguous with last dim divisible by ``group_size``.
+    ``enable_v2`` is accepted and ignored (one kernel here). The masked-layout,
+    fused-SiLU and UE8M0 variants raise NotImplementedError instead of silently differing.
+    """
+    assert x.shape[-1] % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`"
+    assert x.is_contiguous(), "`x` is not contiguous"
+    if scale_ue8m0 or fuse_silu_and_mul or masked_m is not None:
+        raise NotImplementedError("scale_ue8m0 / fuse_silu_and_mul / masked_m are not part of this path")
+    N.require_cuda(x)
+    assert x.dtype in (torch.bfloat16, torch.float16, torch.float32), f"unsupported input dtype {x.dtype}"
+    if column_major_scales:
+        assert x.dim() == 2, "column-major scales need a 2-D input"
+    x_q = torch.empty_like(x, dtype=fp8_dtype)
+    x_s = create_per_token_group_quant_fp8_output_scale(
+        x.shape, x.device, group_size, column_major_scales, scale_tma_aligned, scale_ue8m0
+    )
+    K = x.shape[-1]
+    M = x.numel() // K if K else 0
+    if M > 0:
+        if column_major_scales:
+            sm, sg = x_s.stride(0), x_s.stride(1)
+        else:
+            sm, sg = K // group_size, 1
+        with torch.cuda.device(x.device):
+            st = N.load().b200_per_token_group_quant_fp8(
+                N.ptr(x), N.DTYPE_CODE[x.dtype], N.ptr(x_q), N.ptr(x_s), M, K, group_size, sm, sg, eps,
+                _QUANT_FORMULA, N.current_stream(),
+            )
+        N.check(st, "per_token_group_quant_fp8")
+    return x_q, x_s
+
+
+sglang_per_token_group_quant_fp8 = per_token_group_quant_fp8
+
+
+def prepare_block_fp8_matmul_inputs(
+    A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs: torch.Tensor, block_size: List[int],
+    output_dtype: torch.dtype,
+):
+    """Shape / layout checks of the reference (fp8_kernel.py:1135-1180)."""
+    assert len(block_size) == 2
+    block_n, block_k = block_size
+    assert A.shape[-1] == B.shape[-1]
+    assert A.shape[:-1] == As.shape[:-1]
+    assert A.is_contiguous()
+    assert (A.shape[-1] + block_k - 1) // block_k == As.shape[-1]
+    M = A.numel() // A.shape[-1]
+    assert B.ndim == 2 and B.is_contiguous() and Bs.ndim == 2
+    Nn, K = B.shape
+    assert (Nn + block_n - 1) // block_n == Bs.shape[0]
+    assert (K + block_k - 1) // block_k == Bs.shape[1]
+    C = A.new_empty(A.shape[:-1] + (Nn,), dtype=output_dtype)
+    return M, Nn, K, C
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    """Grow-only per-(device, stream) scratch buffer for the kernels that need one."""
+    if nbytes == 0:
+        return None
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def w8a8_block_fp8_matmul(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    As: torch.Tensor,
+    Bs: torch.Tensor,
+    block_size: List[int],
+    output_dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """``C = sum_kb (A_kb @ B_kb^T) * As[:, kb] * Bs[n//128, kb]`` on the tcgen05 tensor cores.
+
+    Same contract as the reference (fp8_kernel.py:1285-1300): ``A [.., K]`` and ``B [N, K]``
+    FP8 E4M3, contiguous; ``As [.., ceil(K/128)]`` fp32 with any strides (row- or
+    column-major); ``Bs [ceil(N/128), ceil(K/128)]`` fp32. Only ``block_size == [128, 128]``.
+    """
+    M, Nn, K, C = prepare_block_fp8_matmul_inputs(A, B, As, Bs, block_size, output_dtype)
+    if list(block_size) != [128, 128]:
+        raise NotImplementedError("only block_size=[128, 128] is built")
+    N.require_cuda(A, B, As, Bs)
+    assert A.dtype == fp8_dtype and B.dtype == fp8_dtype, "A and B must be float8_e4m3fn"
+    assert output_dtype in (torch.bfloat16, torch.float16, torch.float32)
+    if M == 0 or Nn == 0:
+        return C
+    As2 = As.reshape(M, As.shape[-1]) if As.dim() != 2 else As
+    if As2.dtype != torch.float32:
+        As2 = As2.float()
+    Bs = Bs.float().contiguous() if (Bs.dtype != torch.float32 or not Bs.is_contiguous()) else Bs
+    lib = N.load()
+    ws_bytes = lib.b200_w8a8_block_fp8_gemm_workspace_bytes(M, Nn, K)
+    with torch.cuda.device(A.device):
+        ws = _workspace(A.device, ws_bytes)
+        st = lib.b200_w8a8_block_fp8_gemm(
+            N.ptr(A), N.ptr(As2), As2.stride(0), As2.stride(1), N.ptr(B), N.ptr(Bs), N.ptr(C),
+            N.DTYPE_CODE[output_dtype], M, Nn, K, N.ptr(ws), ws_bytes, N.current_stream(),
+        )
+    N.check(st, "w8a8_block_fp8_matmul")
+    return C
+
+
+def w8a8_block_fp8_linear(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    block_size: List[int],
+    weight_scale: torch.Tensor,
+    input_scale: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Quantise the activation per 1x128 group, run the block GEMM, add the bias: the
+    composition the reference's ``*_w8a8_block_fp8_linear`` wrappers perform
+    (fp8_utils.py:814-834). Scales are produced column-major so the GEMM reads one
+    contiguous run of 128 row-scales per K block."""
+    assert input_scale is None
+    input_2d = input.view(-1, input.shape[-1])
+    output_shape = [*input.shape[:-1], weight.shape[0]]
+    q_input, x_scale = per_token_group_quant_fp8(input_2d, block_size[1], column_major_scales=True)
+    output = w8a8_block_fp8_matmul(q_input, weight, x_scale, weight_scale, block_size, output_dtype=input_2d.dtype)
+    if bias is not None:
+        output += bias
+    return output.to(dtype=input_2d.dtype).view(*output_shape)

@@ -1,0 +1,54 @@
+"""The C-ABI library builds, loads and exports every symbol the header declares (CPU)."""
+import os
+import re
+
+from conftest import ROOT
+
+
+def test_library_exports_every_declared_symbol():
+    from sglang_b200 import _native
+
+    lib = _native.load()
+    header = open(os.path.join(ROOT, "include", "b200_blockfp8.h")).read()
+    declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_native.SIGNATURES), declared ^ set(_native.SIGNATURES)
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.b200_abi_version() == 1
+    assert lib.b200_status_string(0) == b"ok"
+    assert lib.b200_status_string(-5) == b"device-side wait timed out"
+
+
+def test_workspace_queries_need_no_gpu():
+    from sglang_b200 import _native
+
+    lib = _native.load()
+    assert lib.b200_moe_align_workspace_bytes(1024, 257) == 0
+    assert lib.b200_moe_align_workspace_bytes(131072, 257) == 128 * 257 * 4
+    assert lib.b200_w8a8_block_fp8_gemm_workspace_bytes(64, 2048, 2048) == 0
+    assert lib.b200_fused_experts_fp8_workspace_bytes(16, 2, 8, 256, 128) > 0
+
+
+def test_operators_refuse_cpu_tensors():
+    import pytest
+    import torch
+
+    import sglang_b200 as S
+
+    with pytest.raises(RuntimeError):
+        S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16), 128)
+    with pytest.raises(RuntimeError):
+        S.moe_align_block_size(torch.zeros(2, 2, dtype=torch.int32), 16, 8)
+
+
+def test_bad_arguments_return_status_not_crash():
+    from sglang_b200 import _native
+
+    lib = _native.load()
+    st = lib.b200_per_token_group_quant_fp8(None, 0, None, None, 4, 200, 128, 2, 1, 1e-10, 0, None)
+    assert st == _native.E_BAD_ARG and b"null" in lib.b200_last_error_detail()
+    st = lib.b200_w8a8_block_fp8_gemm(None, None, 1, 1, None, None, None, 0, 4, 128, 128, None, 0, None)
+    assert st == _native.E_BAD_ARG
+    st = lib.b200_moe_align_block_size(None, 3, 10, 5000, 16, None, 0, None, 0, None, None, 1, None, 0, None)
+    assert st == _native.E_UNSUPPORTED

@@ -1,0 +1,148 @@
+"""w8a8_block_fp8_matmul (tcgen05 kernel) vs the oracle / the reference's vectors.
+Tolerance: relative Frobenius error <= 1e-2 (the bar stated for this path); fp32 outputs
+are held to 1e-5 because only the summation order differs."""
+import os
+
+import pytest
+import torch
+
+import oracle as O
+from conftest import as_fp8, load_golden, make_activation, make_weight
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _status_ok():
+    from sglang_b200 import _native
+
+    assert _native.read_device_status() == 0, "a bounded device-side wait timed out"
+
+
+def _rand_fp8(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return ((torch.rand(shape, generator=g) - 0.5) * 2 * 448).clamp(-448, 448).to(torch.float8_e4m3fn)
+
+
+def _case(M, N, K, seed, out_dtype=torch.bfloat16, col_major=False, bn=None):
+    import sglang_b200 as S
+
+    g = torch.Generator().manual_seed(seed)
+    A, B = _rand_fp8((M, K), seed), _rand_fp8((N, K), seed + 1)
+    kt, nt = (K + 127) // 128, (N + 127) // 128
+    As = torch.rand(M, kt, generator=g) * 1e-2
+    Bs = torch.rand(nt, kt, generator=g) * 1e-2
+    ref = O.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.float32)
+    As_d = As.cuda()
+    if col_major:
+        As_d = As.t().contiguous().cuda().t()
+        assert As_d.stride() == (1, M)
+    if bn:
+        os.environ["B200_GEMM_BN"] = str(bn)
+    try:
+        C = S.w8a8_block_fp8_matmul(A.cuda(), B.cuda(), As_d, Bs.cuda(), [128, 128], out_dtype)
+        _status_ok()
+    finally:
+        os.environ.pop("B200_GEMM_BN", None)
+    assert C.dtype == out_dtype and tuple(C.shape) == (M, N)
+    err = O.rel_frobenius(C.float().cpu(), ref)
+    assert err < (1e-5 if out_dtype == torch.float32 else TOL), (M, N, K, err)
+    return err
+
+
+def test_reference_vectors():
+    import sglang_b200 as S
+
+    for name, c in load_golden("gemm.npz").items():
+        C = S.w8a8_block_fp8_matmul(
+            as_fp8(c["A"]).cuda(), as_fp8(c["B"]).cuda(), torch.from_numpy(c["As"]).cuda(),
+            torch.from_numpy(c["Bs"]).cuda(), [128, 128], torch.float32,
+        )
+        _status_ok()
+        assert O.rel_frobenius(C.cpu(), torch.from_numpy(c["C"])) < 1e-5, name
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize(
+    "M,N,K", [(1, 128, 128), (7, 256, 512), (128, 384, 1024), (130, 1088, 256), (300, 512, 896), (64, 2048, 2048),
+              (257, 640, 320), (33, 128, 3968)]
+)
+def test_shapes_both_tile_widths(M, N, K, bn):
+    _case(M, N, K, 100 + M + N + K, bn=bn)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_output_dtypes_and_column_major_scales(dtype):
+    _case(83, 512, 512, 5, out_dtype=dtype)
+    _case(83, 512, 512, 6, out_dtype=dtype, col_major=True)
+
+
+def test_many_tiles_persistent_loop():
+    # more tiles than SMs so every CTA walks several tiles and the barrier phases wrap
+    _case(1024, 6144, 1024, 9)
+    _case(2048, 4096, 384, 10, bn=128)
+
+
+def test_config1_quantised_linear():
+    """BASELINE config 1: bf16 [64, 2048] x block-quantised [2048, 2048]."""
+    import sglang_b200 as S
+
+    x = make_activation(64, 2048, 1000, outliers=False)
+    wq, ws = make_weight(2048, 2048, 1001)
+    ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
+    out = S.w8a8_block_fp8_linear(x.cuda(), wq.cuda(), [128, 128], ws.cuda())
+    _status_ok()
+    assert out.dtype == torch.bfloat16
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 14336)])
+def test_llama8b_shapes_small_m(M, N, K):
+    import sglang_b200 as S
+
+    x = make_activation(M, K, 2000 + M)
+    wq, ws = make_weight(N, K, 2001 + N)
+    ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
+    out = S.w8a8_block_fp8_linear(x.cuda(), wq.cuda(), [128, 128], ws.cuda())
+    _status_ok()
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+
+
+def test_full_size_against_dequantised_matmul():
+    """M=8192 x (N=6144, K=4096): too big for the CPU oracle in seconds, so compare with an
+    fp32 matmul of the dequantised operands on the device (same math, other summation order)."""
+    import sglang_b200 as S
+
+    M, N, K = 8192, 6144, 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = ((torch.rand(M, K, device="cuda", generator=g) - 0.5) * 896).to(torch.float8_e4m3fn)
+    B = ((torch.rand(N, K, device="cuda", generator=g) - 0.5) * 896).to(torch.float8_e4m3fn)
+    As = torch.rand(M, K // 128, device="cuda", generator=g) * 1e-2 + 1e-3
+    Bs = torch.rand(N // 128, K // 128, device="cuda", generator=g) * 1e-2 + 1e-3
+    C = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.bfloat16)
+    _status_ok()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    Ad = A.float() * As.repeat_interleave(128, dim=1)
+    Bd = B.float() * Bs.repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)
+    ref = Ad @ Bd.t()
+    err = float((C.float() - ref).norm() / ref.norm())
+    assert err < TOL, err
+    # linearity in the scales: doubling As doubles C exactly (power of two)
+    C2 = S.w8a8_block_fp8_matmul(A, B, As * 2, Bs, [128, 128], torch.bfloat16)
+    assert torch.equal(C2, C * 2)
+
+
+def test_errors():
+    import sglang_b200 as S
+
+    A = torch.zeros(4, 256, device="cuda").to(torch.float8_e4m3fn)
+    B = torch.zeros(128, 256, device="cuda").to(torch.float8_e4m3fn)
+    As = torch.ones(4, 2, device="cuda")
+    Bs = torch.ones(1, 2, device="cuda")
+    with pytest.raises(AssertionError):
+        S.w8a8_block_fp8_matmul(A, B, As[:, :1], Bs, [128, 128])
+    with pytest.raises(NotImplementedError):
+        S.w8a8_block_fp8_matmul(A, B, torch.ones(4, 4, device="cuda"), torch.ones(2, 4, device="cuda"), [64, 64])
+    out = S.w8a8_block_fp8_matmul(A[:0], B, As[:0], Bs, [128, 128], torch.bfloat16)
+    assert out.shape == (0, 128)

@@ -1,0 +1,128 @@
+"""fused_experts(use_fp8_w8a8=True, block_shape=[128,128]) vs the fp32 oracle and the
+reference's vectors. Tolerance: relative Frobenius error <= 1e-2."""
+import pytest
+import torch
+
+import oracle as O
+from conftest import DT, as_fp8, golden_tensor, load_golden
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _status_ok():
+    from sglang_b200 import _native
+
+    assert _native.read_device_status() == 0, "a bounded device-side wait timed out"
+
+
+def _weights(E, I, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    w1 = torch.stack([O.block_quant_weight_fp8((torch.randn(2 * I, H, generator=g) * 0.02).bfloat16())[0] for _ in range(E)])
+    w2 = torch.stack([O.block_quant_weight_fp8((torch.randn(H, I, generator=g) * 0.02).bfloat16())[0] for _ in range(E)])
+    w1_s = torch.rand(E, 2 * I // 128, H // 128, generator=g) * 2e-4 + 1e-4
+    w2_s = torch.rand(E, H // 128, I // 128, generator=g) * 2e-4 + 1e-4
+    return w1, w2, w1_s, w2_s
+
+
+def _run(x, w1, w2, w1_s, w2_s, tw, ti, **cfg):
+    import sglang_b200 as S
+
+    config = S.MoeRunnerConfig(**{"inplace": False, **cfg})
+    out = S.fused_experts(
+        x.cuda(), w1.cuda(), w2.cuda(), S.StandardTopKOutput(tw.cuda(), ti.cuda(), None), config,
+        use_fp8_w8a8=True, w1_scale=w1_s.cuda(), w2_scale=w2_s.cuda(), block_shape=[128, 128],
+    )
+    _status_ok()
+    return out
+
+
+def test_reference_vectors():
+    for name, c in load_golden("moe.npz").items():
+        M, Nn, K, E, topk, code = c["meta"].tolist()
+        a = golden_tensor(c["a"], code)
+        args = (as_fp8(c["w1"]), as_fp8(c["w2"]), torch.from_numpy(c["w1_s"]), torch.from_numpy(c["w2_s"]),
+                torch.from_numpy(c["tw"]), torch.from_numpy(c["ti"]))
+        out = _run(a.bfloat16(), *args)
+        # the stored output was computed by the reference in `code` dtype; the fp32 oracle on
+        # the bf16-rounded input is the tight comparison, the reference vector the loose one
+        ref32 = O.fused_experts_fp8(a.bfloat16(), *args, [128, 128], compute_dtype=torch.float32)
+        assert O.rel_frobenius(out.float().cpu(), ref32) < TOL, name
+        assert O.rel_frobenius(out.float().cpu(), torch.from_numpy(c["out"])) < 3e-2, name
+
+
+@pytest.mark.parametrize(
+    "T,E,topk,H,I", [(1, 8, 2, 256, 128), (33, 8, 2, 512, 256), (64, 8, 2, 1024, 512), (200, 32, 8, 512, 256),
+                     (1024, 8, 2, 512, 384), (129, 64, 6, 256, 128)]
+)
+def test_shapes_vs_fp32_oracle(T, E, topk, H, I):
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 7 + T)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), topk, True)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti)
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (T, H)
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+
+
+def test_expert_parallel_minus_one_ids_sum_to_full_result():
+    T, E, topk, H, I = 96, 16, 4, 512, 256
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 12)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), topk, True)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    total = torch.zeros(T, H)
+    for r in range(4):
+        lo, hi = r * 4, r * 4 + 4
+        local = O.ep_local_expert_ids(ti, E, 4, r)
+        part = _run(x, w1[lo:hi], w2[lo:hi], w1_s[lo:hi], w2_s[lo:hi], tw, local, num_experts=E, num_local_experts=4)
+        ref_part = O.fused_experts_fp8(x, w1[lo:hi], w2[lo:hi], w1_s[lo:hi], w2_s[lo:hi], tw, local, [128, 128])
+        assert O.rel_frobenius(part.float().cpu(), ref_part) < TOL
+        total += part.float().cpu()
+    assert O.rel_frobenius(total, ref) < TOL
+    # a rank that owns none of the selected experts returns exact zeros
+    none = _run(x, w1[:4], w2[:4], w1_s[:4], w2_s[:4], tw, torch.full_like(ti, -1))
+    assert none.abs().max().item() == 0
+
+
+def test_flags_inplace_no_combine_scaling_weight_on_input():
+    import sglang_b200 as S
+
+    T, E, topk, H, I = 50, 8, 2, 256, 128
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 22)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), topk, True)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti, routed_scaling_factor=2.5)
+    assert O.rel_frobenius(out.float().cpu(), ref * 2.5) < TOL
+    nc = _run(x, w1, w2, w1_s, w2_s, tw, ti, no_combine=True)
+    ref_nc = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128], no_combine=True)
+    assert tuple(nc.shape) == (T, topk, H) and O.rel_frobenius(nc.float().cpu(), ref_nc) < TOL
+    xd = x.cuda()
+    res = S.fused_experts(
+        xd, w1.cuda(), w2.cuda(), S.StandardTopKOutput(tw.cuda(), ti.cuda(), None), S.MoeRunnerConfig(),
+        use_fp8_w8a8=True, w1_scale=w1_s.cuda(), w2_scale=w2_s.cuda(), block_shape=[128, 128],
+    )
+    assert res.data_ptr() == xd.data_ptr() and O.rel_frobenius(xd.float().cpu(), ref) < TOL
+    tw1, ti1 = O.softmax_topk(torch.randn(T, E, generator=g), 1, False)
+    ref1 = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw1, ti1, [128, 128], apply_router_weight_on_input=True)
+    out1 = _run(x, w1, w2, w1_s, w2_s, tw1, ti1, apply_router_weight_on_input=True)
+    assert O.rel_frobenius(out1.float().cpu(), ref1) < 2e-2  # weighting rounds the input to bf16 first
+    with pytest.raises(NotImplementedError):
+        S.fused_experts(xd, w1.cuda(), w2.cuda(), S.StandardTopKOutput(tw.cuda(), ti.cuda(), None),
+                        S.MoeRunnerConfig(), use_fp8_w8a8=False)
+
+
+def test_deepseek_routing_skewed_load():
+    """256 experts, top-8 grouped sigmoid routing (reduced hidden sizes so the oracle is quick)."""
+    T, E, topk, H, I = 300, 256, 8, 512, 256
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 32)
+    tw, ti = O.biased_grouped_topk(torch.randn(T, E, generator=g), torch.zeros(E), topk, 8, 4, True)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti)
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL

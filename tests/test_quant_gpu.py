@@ -1,0 +1,91 @@
+"""per_token_group_quant_fp8 on the GPU vs the oracle and the reference's vectors: bit-exact."""
+import pytest
+import torch
+
+import oracle as O
+from conftest import golden_tensor, load_golden, make_activation
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(x_cpu, group, **kw):
+    import sglang_b200 as S
+
+    q, s = S.per_token_group_quant_fp8(x_cpu.cuda(), group, **kw)
+    rq, rs = O.per_token_group_quant_fp8(x_cpu, group)
+    assert q.dtype == torch.float8_e4m3fn and s.dtype == torch.float32
+    assert tuple(s.shape) == tuple(rs.shape)
+    assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+    assert torch.equal(s.cpu(), rs)
+    return q, s
+
+
+def test_reference_vectors_bit_exact():
+    import sglang_b200 as S
+
+    for name, c in load_golden("quant.npz").items():
+        m, d, g, code = c["meta"].tolist()
+        x = golden_tensor(c["x"], code)
+        q, s = S.per_token_group_quant_fp8(x.cuda(), g)
+        assert torch.equal(q.cpu().view(torch.uint8), torch.from_numpy(c["q"])), name
+        assert torch.equal(s.cpu(), torch.from_numpy(c["s"])), name
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("group", [16, 32, 64, 128, 256, 512])
+@pytest.mark.parametrize("M,K", [(1, 512), (7, 1024), (83, 4096), (333, 1536)])
+def test_shapes_groups_dtypes(M, K, group, dtype):
+    _check(make_activation(M, K, 1000 * M + K, dtype), group)
+
+
+@pytest.mark.parametrize("M", [1, 3, 64, 130])
+def test_scale_layouts(M):
+    x = make_activation(M, 2048, 7 + M)
+    q, s = _check(x, 128, column_major_scales=True)
+    assert s.stride() == (1, M)
+    q, s = _check(x, 128, column_major_scales=True, scale_tma_aligned=True)
+    assert s.stride() == (1, (M + 3) // 4 * 4)
+
+
+def test_all_zero_group_and_extremes():
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    x[1, 5] = -3.0
+    x[2, 128:] = 1e-20
+    x[3, :] = 6e4
+    q, s = _check(x, 128)
+    assert s[0, 0].item() == (torch.tensor(1e-10) / 448).item()
+
+
+def test_config1_and_large_row_count():
+    _check(make_activation(64, 2048, 1000), 128)
+    _check(make_activation(8192, 4096, 2000), 128)
+
+
+def test_formula_variants():
+    import sglang_b200 as S
+
+    x = make_activation(33, 1024, 5)
+    try:
+        for f in (1, 2):
+            S.set_quant_formula(f)
+            q, s = S.per_token_group_quant_fp8(x.cuda(), 128)
+            rq, rs = O.per_token_group_quant_fp8(x, 128, formula=f)
+            assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+            assert torch.equal(s.cpu(), rs)
+    finally:
+        S.set_quant_formula(0)
+
+
+def test_empty_and_errors():
+    import sglang_b200 as S
+
+    q, s = S.per_token_group_quant_fp8(torch.empty(0, 256, dtype=torch.bfloat16, device="cuda"), 128)
+    assert q.shape == (0, 256) and s.shape == (0, 2)
+    with pytest.raises(AssertionError):
+        S.per_token_group_quant_fp8(torch.zeros(2, 200, dtype=torch.bfloat16, device="cuda"), 128)
+    with pytest.raises(AssertionError):
+        S.per_token_group_quant_fp8(torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda").t(), 128)
+    with pytest.raises(NotImplementedError):
+        S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16, device="cuda"), 128, scale_ue8m0=True)
+    with pytest.raises(RuntimeError):
+        S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16), 128)
