@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Benchmark of the block-FP8 W8A8 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1 and every N): the four Llama-3-8B-shaped block-FP8 linears -- qkv
+(6144x4096), o_proj (4096x4096), gate_up (28672x4096), down (4096x14336) -- at M = 8192
+rows. One step = per-token-group quantisation + block-FP8 GEMM for each of the four, i.e.
+one pass of the quantised-linear hot path over one batch. Inputs are seeded synthetic
+tensors (N(0,1) activations with 1% outlier channels x20, N(0, 0.02^2) weights
+block-quantised 128x128); there is no dataset. With N > 1 every rank processes its own
+batch (no data-path collective: weak scaling); the tensor-/expert-parallel variants are
+reported as extra keys.
+
+`value`    TFLOP/s (2*M*N*K summed over the four GEMMs, all ranks) with inputs resident in HBM.
+`e2e`      the same metric through the public operators with HOST buffers: pinned host ->
+           device copy of the activations and device -> host copy of the outputs inside
+           the timed region, every step.
+`roofline` the GEMM kernel's achieved TFLOP/s (CUDA events around its launches in the timed
+           steps) against 2 x the measured dense bf16 rate (FP8 issues at twice the bf16 rate;
+           MEASURED_PEAKS.json holds no FP8 entry).
+`cpu_baseline` the oracle's torch-native restatement of the reference path on the host cores,
+           on a bounded sample (fewer rows) of the same workload.
+`--impl reference` times that CPU path alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+M_ROWS = 8192
+LINEARS = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
+FLOPS_PER_ROW = sum(2 * n * k for _, n, k in LINEARS)
+WORKLOAD = "llama3-8b block-fp8 linears (qkv,o_proj,gate_up,down), M=8192: quant + GEMM each"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while a timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_workload(device, rank: int):
+    """Seeded CPU tensors -> pinned host copies + device copies. Seeds: 2000 + index (+ rank)."""
+    from sglang_b200 import synthetic
+
+    acts_host, acts_dev, weights = {}, {}, {}
+    for i, (name, n, k) in enumerate(LINEARS):
+        x = synthetic.activation(M_ROWS, k, 2000 + 10 * i + 100 * rank).pin_memory()
+        acts_host[name] = x
+        acts_dev[name] = x.to(device, non_blocking=True)
+        weights[name] = synthetic.weight(n, k, 2001 + 10 * i, device=device)
+    torch.cuda.synchronize()
+    return acts_host, acts_dev, weights
+
+
+def run_step(S, acts, weights, gemm_events=None):
+    outs = {}
+    for name, n, k in LINEARS:
+        wq, ws = weights[name]
+        q, s = S.per_token_group_quant_fp8(acts[name], 128, column_major_scales=True)
+        if gemm_events is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        outs[name] = S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)
+        if gemm_events is not None:
+            e1.record()
+            gemm_events.append((name, e0, e1))
+    return outs
+
+
+def dist_max(value: float, world: int, device) -> float:
+    if world == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def cpu_linears(rows: int, threads: int, weights_cpu, acts_cpu):
+    """One pass of the four linears through the oracle (torch-native reference restatement)."""
+    import oracle as O
+
+    torch.set_num_threads(threads)
+    for name, n, k in LINEARS:
+        wq, ws = weights_cpu[name]
+        O.w8a8_block_fp8_linear(acts_cpu[name][:rows], wq, ws, output_dtype=torch.bfloat16)
+
+
+def cpu_inputs(rows: int):
+    """Same seeds as the GPU workload; weights quantised by the package's quantiser (bit-identical
+    to the oracle's, see tests)."""
+    from sglang_b200 import synthetic
+
+    acts, weights = {}, {}
+    for i, (name, n, k) in enumerate(LINEARS):
+        acts[name] = synthetic.activation(rows, k, 2000 + 10 * i)
+        weights[name] = synthetic.weight(n, k, 2001 + 10 * i)
+    return acts, weights
+
+
+def time_cpu_baseline(budget_s: float = 15.0):
+    """Oracle on the host cores on a bounded row sample sized to ~budget_s of CPU work."""
+    threads = os.cpu_count() or 1
+    rows = 64
+    acts, weights = cpu_inputs(256)
+    t0 = time.perf_counter()
+    cpu_linears(rows, threads, weights, acts)
+    dt = time.perf_counter() - t0
+    # scale the sample towards the budget (the first pass doubles as warm-up)
+    rows = int(max(64, min(256, rows * budget_s / max(dt, 1e-3) / 2)))
+    rows = rows // 32 * 32
+    t0 = time.perf_counter()
+    cpu_linears(rows, threads, weights, acts)
+    dt = time.perf_counter() - t0
+    return {"value": rows * FLOPS_PER_ROW / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"the four linears on the first {rows} of {M_ROWS} rows, one pass, {dt:.1f} s (torch fp32, oracle/)"}
+
+
+def run_reference(args, rank: int):
+    """The reference's CPU implementation of the path (its torch-native functions, restated in
+    oracle/ and pinned to them by the golden vectors) on all host threads."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = 64
+    acts, weights = cpu_inputs(rows)
+    for _ in range(args.warmup):
+        cpu_linears(rows, threads, weights, acts)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_linears(rows, threads, weights, acts)
+    dt = (time.perf_counter() - t0) / args.steps
+    v = rows * FLOPS_PER_ROW / dt / 1e12
+    sample = f"each step = the four linears on {rows} of {M_ROWS} rows (torch fp32 on {threads} threads)"
+    print(json.dumps({
+        "impl": "reference", "metric": "block-FP8 GEMM TFLOPS", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 weights+activations, fp32 accumulate (emulated in fp32 on CPU)",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "rows_per_step": rows},
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def bench_moe(S, device, steps: int):
+    """Extra line items: fused-MoE tokens/s for the DeepSeek-V3 and Mixtral shaped layers (1 GPU)."""
+    from sglang_b200 import synthetic
+    from sglang_b200.topk import biased_grouped_topk, fused_topk
+
+    out = {}
+    for label, cfg, T in (("deepseek_v3_T16384", synthetic.DEEPSEEK_V3, 16384), ("mixtral_8x7b_T8192", synthetic.MIXTRAL, 8192)):
+        E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
+        w1, w2, w1_s, w2_s = synthetic.expert_weights(E, I, H, 4000 + E, device=device)
+        g = torch.Generator().manual_seed(5000 + T)
+        x = torch.randn(T, H, generator=g).bfloat16().to(device)
+        if E == 256:
+            logits = torch.randn(T, E, generator=g).to(device)
+            tw, ti = biased_grouped_topk(x, logits, torch.zeros(E, device=device), topk, True, cfg["n_group"], cfg["topk_group"])
+        else:
+            logits = synthetic.zipf_router_logits(T, E, 5001).to(device)
+            tw, ti = fused_topk(x, logits, topk, True)
+        conf = S.MoeRunnerConfig(inplace=False)
+        topk_out = S.StandardTopKOutput(tw, ti, None)
+
+        def call():
+            return S.fused_experts(x, w1, w2, topk_out, conf, use_fp8_w8a8=True, w1_scale=w1_s, w2_scale=w2_s, block_shape=[128, 128])
+
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out[label] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "tflops": 6 * T * topk * H * I / ms / 1e9,
+                      "config": {"E": E, "topk": topk, "H": H, "I": I, "T": T, "weights_mb": (w1.numel() + w2.numel()) / 1e6}}
+        del w1, w2, w1_s, w2_s
+        torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the MoE / cpu-baseline line items")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    import sglang_b200 as S
+    from sglang_b200 import _native
+
+    peaks = load_peaks()
+    acts_host, acts_dev, weights = build_workload(device, rank)
+
+    # ---------------------------------------------------------------- device-resident timing
+    for _ in range(args.warmup):
+        run_step(S, acts_dev, weights)
+    gemm_events = []
+    barrier(world)
+    with ClockSampler(local_rank) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run_step(S, acts_dev, weights, gemm_events)
+        e1.record()
+        barrier(world)
+    ms_step = dist_max(e0.elapsed_time(e1) / args.steps, world, device)
+    status = _native.read_device_status()
+    if status != 0:
+        raise SystemExit(f"device status word = {status}: a bounded wait timed out; the numbers are void")
+    value = world * M_ROWS * FLOPS_PER_ROW / ms_step / 1e9
+
+    per_shape = {}
+    for name, a, b in gemm_events:
+        per_shape.setdefault(name, []).append(a.elapsed_time(b))
+    gemm_ms = sum(statistics.mean(v) for v in per_shape.values())
+    gemm_tflops = M_ROWS * FLOPS_PER_ROW / gemm_ms / 1e9
+    fp8_peak = 2 * peaks["bf16_sustained"]
+    roofline = {"bound": "tensor", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
+                "traffic": None, "kernel": "block_fp8_gemm_kernel<256,dense,bf16>",
+                "peak_note": f"2 x {peaks['source']} sustained dense bf16 ({peaks['bf16_sustained']} TF/s); nominal dense FP8 is 4500",
+                "frac_of_nominal_fp8": gemm_tflops / 4500.0,
+                "per_shape_tflops": {n: 2 * M_ROWS * nn * kk / statistics.mean(per_shape[n]) / 1e9 for n, nn, kk in LINEARS}}
+
+    # ------------------------------------------------------------------ end-to-end (host buffers)
+    outs_host = {name: torch.empty(M_ROWS, n, dtype=torch.bfloat16).pin_memory() for name, n, k in LINEARS}
+    h2d = sum(x.numel() * x.element_size() for x in acts_host.values())
+    d2h = sum(x.numel() * x.element_size() for x in outs_host.values())
+
+    def e2e_step():
+        dev = {name: acts_host[name].to(device, non_blocking=True) for name, _, _ in LINEARS}
+        outs = run_step(S, dev, weights)
+        for name, _, _ in LINEARS:
+            outs_host[name].copy_(outs[name], non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier(world)
+    e2e_ms = dist_max(e0.elapsed_time(e1) / e2e_steps, world, device)
+    e2e = {"value": world * M_ROWS * FLOPS_PER_ROW / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    line = {
+        "metric": "block-FP8 GEMM TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 accumulate, bf16 out", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": M_ROWS, "block_shape": [128, 128],
+                   "l2": "per-step working set 1.4 GB (weights 218 MB + activations 436 MB + outputs 705 MB) > 126 MB L2",
+                   "parallelism": f"{world} independent replicas" if world > 1 else "single GPU"},
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": args.steps * 2 * len(LINEARS), "roofline": roofline,
+    }
+    if rank == 0 and not args.no_extras:
+        del acts_dev, outs_host
+        torch.cuda.empty_cache()
+        if world == 1:
+            try:
+                line["moe"] = bench_moe(S, device, steps=5)
+            except Exception as e:  # the headline number stands without the extra line items
+                line["moe"] = {"error": repr(e)}
+        line["cpu_baseline"] = time_cpu_baseline()
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -88,10 +88,12 @@ def per_token_group_quant_fp8(
         q = xf / s
     elif formula == 1:
         s = amax / FP8_MAX
-        q = xf * (1.0 / s)
+        q = xf * (torch.ones_like(s) / s)
     elif formula == 2:
         s = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32)
-        q = xf * (FP8_MAX / amax)
+        # tensor / tensor: one IEEE division, as `MAX / amax` in the kernel (a Python scalar
+        # divided by a tensor would be reciprocal-then-multiply, i.e. rounded twice)
+        q = xf * (torch.full_like(amax, FP8_MAX) / amax)
     else:
         raise ValueError(f"unknown formula {formula}")
     q = q.clamp(min=FP8_MIN, max=FP8_MAX).to(FP8).reshape(x.shape)
@@ -242,7 +244,6 @@ def fused_experts_fp8(
     a = a.to(compute_dtype)
     if apply_router_weight_on_input:
         assert topk == 1
-        a = a * topk_weights.to(compute_dtype)
     a_rep = a.view(T, 1, D).repeat(1, topk, 1).reshape(-1, D)
     out = torch.zeros(T * topk, w2.shape[1], dtype=compute_dtype)
     ids = topk_ids.reshape(-1)
@@ -252,6 +253,10 @@ def fused_experts_fp8(
         mask = ids == e
         if mask.sum():
             inter = w8a8_block_fp8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, output_dtype=compute_dtype)
+            if apply_router_weight_on_input:
+                # the reference's first grouped GEMM multiplies its fp32 accumulator by the router
+                # weight (fused_moe_triton_kernels.py:602-604 with mul_routed_weight set for GEMM 1)
+                inter = inter * topk_weights.reshape(-1)[mask].view(-1, 1).to(inter.dtype)
             act = silu_and_mul(inter)
             act_q, act_s = per_token_group_quant_fp8(act.contiguous(), bk)
             out[mask] = w8a8_block_fp8_matmul(act_q, w2[e], act_s, w2_s[e], block_shape, output_dtype=compute_dtype)

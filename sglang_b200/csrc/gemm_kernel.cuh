@@ -45,7 +45,7 @@ struct GemmParams {
   const int32_t* expert_ids;    // [m_tiles] expert of every 128-row block, -1 = skip
   const int32_t* num_post_pad;  // [1] live rows (multiple of 128)
   const int32_t* sorted_ids;    // [M] flat (token*topk+slot) index of every row, >= numel = pad
-  const float* topk_weights;    // [numel] (MODE 2; may be null = no weighting)
+  const float* topk_weights;    // [numel] router weight per (token, slot); null = no weighting in this GEMM
   int numel;
   // MODE 1 outputs: FP8 activation [M, N] (N = intermediate size I; B holds 2I rows per
   // expert) and its scales, column-major: q_scales[(n/128)*q_scale_ld + row]
@@ -303,6 +303,14 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
       // ------------------------------------------------------------ tile epilogue
       if (MODE == GEMM_GROUPED_SILU_QUANT) {
+        if (p.topk_weights != nullptr) {
+          // router weight applied to the gate_up product in fp32, before the activation (where
+          // the reference's first grouped GEMM applies it when apply_router_weight_on_input is set)
+          const int flat = row_ok ? p.sorted_ids[row] : p.numel;
+          const float w = flat < p.numel ? __ldg(p.topk_weights + flat) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 128; ++j) acc[j] *= w;
+        }
         // warps 4-7 hold `up`, warps 0-3 hold `gate` of the same rows and columns: hand `up`
         // over through shared memory 64 columns at a time ([column][row]: conflict free).
 #pragma unroll

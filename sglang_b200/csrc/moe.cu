@@ -21,7 +21,7 @@ constexpr int kMoeBlockM = 128;
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
     const T* __restrict__ hidden, const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
-    const int32_t* __restrict__ num_post_pad, const float* __restrict__ in_weights, uint8_t* __restrict__ q,
+    const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q,
     float* __restrict__ s, int64_t total_chunks, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t slot = c / chunks_per_row;
@@ -34,11 +34,6 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
   float f[16];
   if (real) {
     Vec16<T>::load(hidden + (int64_t)(flat / topk) * H + chunk * 16, f);
-    if (in_weights != nullptr) {
-      const float w = __ldg(in_weights + flat);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) f[i] = to_f32<T>(from_f32<T>(f[i] * w));  // reference rounds to the input dtype
-    }
   } else {
 #pragma unroll
     for (int i = 0; i < 16; ++i) f[i] = 0.f;
@@ -144,8 +139,7 @@ static int run_fused_experts(const void* hidden, const void* w1, const void* w2,
     const int cpr = (int)(H / 16);
     const int64_t total = L.cap * cpr;
     moe_gather_quant_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
-        static_cast<const T*>(hidden), sorted, expert_ids, npp, weight_on_input ? topk_weights : nullptr, aq1, as1,
-        total, cpr, H, (int)numel, topk, L.cap);
+        static_cast<const T*>(hidden), sorted, expert_ids, npp, aq1, as1, total, cpr, H, (int)numel, topk, L.cap);
     if ((rc = check_launch("moe_gather_quant"))) return rc;
   }
   int force_bn = 0;
@@ -157,7 +151,7 @@ static int run_fused_experts(const void* hidden, const void* w1, const void* w2,
   p.M = (int)L.cap;
   // GEMM 1: [cap, H] x w1[E, 2I, H]^T -> silu(gate)*up -> FP8 [cap, I] + column-major scales
   p.As = as1; p.as_sm = 1; p.as_sk = L.cap; p.Bs = w1_scale; p.C = nullptr; p.ldc = 0;
-  p.N = (int)I; p.K = (int)H; p.topk_weights = nullptr;
+  p.N = (int)I; p.K = (int)H; p.topk_weights = weight_on_input ? topk_weights : nullptr;
   p.q_out = aq2; p.q_scales = as2; p.q_scale_ld = L.cap;
   if ((rc = launch_gemm<GEMM_GROUPED_SILU_QUANT, T>(aq1, w1, (int64_t)E * 2 * I, p, 256, st, tiles_hint))) return rc;
   // GEMM 2: [cap, I] x w2[E, H, I]^T -> rows scattered to (token, slot), times the router weight

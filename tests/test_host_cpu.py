@@ -1,0 +1,49 @@
+"""Host-side pieces that need no GPU: weight quantiser, routing, synthetic inputs."""
+import torch
+
+import oracle as O
+from conftest import golden_tensor, load_golden
+
+
+def test_package_weight_quantiser_is_bit_identical_to_oracle_and_reference():
+    from sglang_b200.weight_quant import block_dequant_weight, block_quant_weight_fp8
+
+    c = load_golden("weight_quant.npz")["w"]
+    w = golden_tensor(c["w"], 0)
+    q, s = block_quant_weight_fp8(w)
+    assert torch.equal(q.view(torch.uint8), torch.from_numpy(c["q"])) and torch.equal(s, torch.from_numpy(c["s"]))
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(200, 300, generator=g) * 0.02).bfloat16()  # ragged: pads to 256 x 384
+    q, s = block_quant_weight_fp8(w)
+    oq, os_ = O.block_quant_weight_fp8(w)
+    assert torch.equal(q.view(torch.uint8), oq.view(torch.uint8)) and torch.equal(s, os_)
+    assert (block_dequant_weight(q, s) - w.float()).abs().max() < 0.02 * 4 / 8
+
+
+def test_routing_matches_reference_vectors():
+    from sglang_b200.topk import biased_grouped_topk, fused_topk
+
+    c = load_golden("routing.npz")
+    logits = torch.from_numpy(c["softmax"]["logits"])
+    w, ids = fused_topk(torch.zeros(logits.shape[0], 4), logits, 2, True)
+    assert torch.equal(w, torch.from_numpy(c["softmax"]["w"])) and torch.equal(ids, torch.from_numpy(c["softmax"]["ids"]))
+    g = c["grouped"]
+    logits = torch.from_numpy(g["logits"])
+    w, ids = biased_grouped_topk(torch.zeros(logits.shape[0], 4), logits, torch.from_numpy(g["bias"]), 8, True, 8, 4)
+    assert torch.equal(w, torch.from_numpy(g["w"])) and torch.equal(ids, torch.from_numpy(g["ids"]))
+
+
+def test_synthetic_inputs_are_seeded_and_shaped():
+    from sglang_b200 import synthetic
+
+    a = synthetic.activation(16, 4096, 7)
+    b = synthetic.activation(16, 4096, 7)
+    assert torch.equal(a, b) and a.dtype == torch.bfloat16
+    col_amax = a.float().abs().amax(dim=0)
+    assert (col_amax > 10).sum() >= 30  # ~1% of 4096 channels carry x20 outliers
+    wq, ws = synthetic.weight(256, 384, 3)
+    assert wq.dtype == torch.float8_e4m3fn and tuple(ws.shape) == (2, 3)
+    lg = synthetic.zipf_router_logits(4096, 8, 1)
+    _, ids = O.softmax_topk(lg, 2, True)
+    counts = torch.bincount(ids.flatten().long(), minlength=8).float()
+    assert counts.max() / counts.min().clamp(min=1) > 3  # skewed load
