@@ -105,15 +105,19 @@ int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel
  * replaces: python/sglang/srt/layers/moe/moe_runner/triton_utils/fused_moe.py:218-306
  *           (kernel sequence :401-785: align -> quant -> grouped GEMM -> silu_and_mul ->
  *            quant -> grouped GEMM * topk_weight -> sum over top-k)
- * hidden [T,H] (h_dtype bf16/f16), w1 [E,2I,H] e4m3 (gate rows [0,I), up rows [I,2I)),
+ * hidden [T,H] (h_dtype bf16/f16); or, when hidden_scale != NULL, hidden is ALREADY quantised:
+ * e4m3 bytes [T,H] with row-major fp32 scales hidden_scale [T,H/128] (what an expert-parallel
+ * dispatch delivers, python/sglang/srt/layers/moe/token_dispatcher/deepep.py:507-567) and
+ * h_dtype is the dtype of `out` only. w1 [E,2I,H] e4m3 (gate rows [0,I), up rows [I,2I)),
  * w2 [E,H,I] e4m3, w1_scale fp32 [E,2I/128,H/128], w2_scale fp32 [E,H/128,I/128],
  * topk_weights fp32 [T,topk], topk_ids int32 [T,topk] with values in [-1,E) (-1 = expert
  * not on this rank: contributes 0). out [T,H] (or [T,topk,H] when no_combine != 0), h_dtype;
- * out may alias hidden (the reference's inplace=True). H % 128 == 0, I % 128 == 0.
+ * out may alias a 16-bit hidden (the reference's inplace=True). H % 128 == 0, I % 128 == 0.
  * routed_scaling_factor multiplies the combined output (pass 1.0f for none).
  * workspace: b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I) bytes, 256-B aligned. */
 size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, int E, int64_t H, int64_t I);
-int b200_fused_experts_fp8(const void* hidden, int h_dtype, const void* w1, const void* w2,
+int b200_fused_experts_fp8(const void* hidden, const float* hidden_scale, int h_dtype,
+                           const void* w1, const void* w2,
                            const float* w1_scale, const float* w2_scale,
                            const float* topk_weights, const int32_t* topk_ids, void* out,
                            int64_t T, int topk, int E, int64_t H, int64_t I, int no_combine,

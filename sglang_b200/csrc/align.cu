@@ -230,7 +230,8 @@ extern "C" int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, in
   B200_CHECK_ARG(num_buckets >= 1 && block_size >= 1, "align: num_buckets=%d block_size=%d", num_buckets, block_size);
   B200_UNSUPPORTED(num_buckets > kMaxBuckets, "align: more than %d buckets", kMaxBuckets);
   B200_UNSUPPORTED(numel >= (1LL << 30), "align: numel too large for int32 positions");
-  B200_CHECK_ARG(sorted_token_ids && expert_ids && num_post_pad && cumsum, "align: null output");
+  B200_CHECK_ARG(num_post_pad && cumsum, "align: null output");
+  B200_CHECK_ARG((sorted_token_ids || max_pad == 0) && (expert_ids || max_blocks == 0), "align: null output");
   B200_CHECK_ARG(numel == 0 || topk_ids, "align: null topk_ids");
   // worst case every bucket needs block_size-1 pads
   B200_CHECK_ARG(max_pad >= 0 && max_blocks * block_size >= 0, "align: bad output sizes");

@@ -66,6 +66,8 @@ struct GemmCfg {
   static constexpr int kStageB = BN * kBK;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
+  // one CTA per SM: 65536 registers / threads, rounded down to the allocation unit of 8
+  static constexpr int kMaxRegs = BN == 256 ? 200 : 255;
   static constexpr int kExchangeBytes = 64 * kBM * 4;  // MODE 1: 64 columns x 128 rows of fp32
   static constexpr size_t smem_bytes(int mode) {
     return (size_t)kStages * (kStageA + kStageB) + (mode == 1 ? kExchangeBytes : 0) + 1024 /*align slack*/ +
@@ -110,6 +112,17 @@ __device__ __forceinline__ void store8<float>(float* dst, const float* a) {
   *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
 }
 
+// acc[0..32) += v[0..32) * scale, two lanes of fp32 per instruction (packed FFMA2 on sm_100).
+__device__ __forceinline__ void promote32(float* acc, const uint32_t (&v)[32], float2 sc2) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float2 r = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), sc2,
+                                make_float2(acc[2 * j], acc[2 * j + 1]));
+    acc[2 * j] = r.x;
+    acc[2 * j + 1] = r.y;
+  }
+}
+
 // tile index -> (m_tile, n_tile): sweep group_m row-tiles for every column tile before moving
 // on, so the CTAs running together share A rows and B columns in L2.
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
@@ -123,7 +136,7 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 }
 
 template <int BN, int MODE, typename OutT>
-__global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
+__global__ void __maxnreg__(GemmCfg<BN>::kMaxRegs)
 block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -267,37 +280,50 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      float sc_next = row_ok ? __ldg(as_ptr) * __ldg(bs_ptr) : 0.f;
+      // Scales are fetched four K blocks ahead (an L2 round trip is longer than one K block of
+      // MMA) and multiplied only when used, so no iteration waits on a load it just issued.
+      float a_pf[4], b_pf[4];
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const bool in = row_ok && d < num_kb;
+        a_pf[d] = in ? __ldg(as_ptr + (int64_t)d * p.as_sk) : 0.f;
+        b_pf[d] = in ? __ldg(bs_ptr + d) : 0.f;
+      }
 
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int b = it & 1;
-        const float sc = sc_next;
-        if (kb + 1 < num_kb) sc_next = row_ok ? __ldg(as_ptr + (int64_t)(kb + 1) * p.as_sk) * __ldg(bs_ptr + kb + 1) : 0.f;
+        const float sc = a_pf[0] * b_pf[0];
+        const float2 sc2 = make_float2(sc, sc);
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+          a_pf[d] = a_pf[d + 1];
+          b_pf[d] = b_pf[d + 1];
+        }
+        {
+          const bool in = row_ok && kb + 4 < num_kb;
+          a_pf[3] = in ? __ldg(as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
+          b_pf[3] = in ? __ldg(bs_ptr + kb + 4) : 0.f;
+        }
         ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
         if (!ok) break;
         ptx::tc_fence_after();
         const uint32_t ta = lane_base + b * BN;
         uint32_t va[32], vb[32];
+        // two TMEM loads in flight per wait; the second pair overlaps the FMAs of the first
         ptx::tmem_ld32(ta, va);
-        ptx::tmem_ld_wait(va);
         ptx::tmem_ld32(ta + 32, vb);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(va[j]), sc, acc[j]);
-        ptx::tmem_ld_wait(vb);
+        ptx::tmem_ld_wait2(va, vb);
+        promote32(acc, va, sc2);
         ptx::tmem_ld32(ta + 64, va);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(vb[j]), sc, acc[32 + j]);
-        ptx::tmem_ld_wait(va);
+        promote32(acc + 32, vb, sc2);
         ptx::tmem_ld32(ta + 96, vb);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(__uint_as_float(va[j]), sc, acc[64 + j]);
-        ptx::tmem_ld_wait(vb);
+        ptx::tmem_ld_wait2(va, vb);
         // every TMEM read of this buffer has landed: give it back to the MMA warp
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(__uint_as_float(vb[j]), sc, acc[96 + j]);
+        promote32(acc + 64, va, sc2);
+        promote32(acc + 96, vb, sc2);
       }
       if (!ok) break;
 

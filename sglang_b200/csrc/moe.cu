@@ -50,6 +50,29 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
   }
 }
 
+// Pre-quantised input (expert-parallel dispatch delivers FP8 rows + 1x128 scales): plain
+// gather of bytes and scales into the expert-sorted layout. One thread = 16 bytes of a row.
+__global__ void __launch_bounds__(256) moe_gather_fp8_kernel(
+    const uint8_t* __restrict__ hidden_q, const float* __restrict__ hidden_s, const int32_t* __restrict__ sorted_ids,
+    const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q,
+    float* __restrict__ s, int64_t total_chunks, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t slot = c / chunks_per_row;
+  const int chunk = (int)(c - slot * chunks_per_row);
+  if (c >= total_chunks || slot >= *num_post_pad) return;
+  if (expert_ids[slot / kMoeBlockM] < 0) return;
+  const int flat = sorted_ids[slot];
+  uint4 v = make_uint4(0, 0, 0, 0);
+  float sc = 0.f;
+  if (flat < numel) {
+    const int64_t tok = flat / topk;
+    v = ld_nc_16(hidden_q + tok * H + chunk * 16);
+    if ((chunk & 7) == 0) sc = __ldg(hidden_s + tok * (H / 128) + chunk / 8);
+  }
+  *reinterpret_cast<uint4*>(q + slot * H + chunk * 16) = v;
+  if ((chunk & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot] = sc;
+}
+
 // out[t, :] = scale * sum_j y[t*topk + j, :] over the slots whose expert id is valid.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_sum_reduce_kernel(const T* __restrict__ y, const int32_t* __restrict__ topk_ids,
@@ -107,7 +130,7 @@ static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, 
 }
 
 template <typename T>
-static int run_fused_experts(const void* hidden, const void* w1, const void* w2, const float* w1_scale,
+static int run_fused_experts(const void* hidden, const float* hidden_scale, const void* w1, const void* w2, const float* w1_scale,
                              const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
                              int64_t T_tokens, int topk, int E, int64_t H, int64_t I, int no_combine,
                              int weight_on_input, float routed_scale, uint8_t* ws, cudaStream_t st) {
@@ -138,9 +161,14 @@ static int run_fused_experts(const void* hidden, const void* w1, const void* w2,
   {
     const int cpr = (int)(H / 16);
     const int64_t total = L.cap * cpr;
-    moe_gather_quant_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
-        static_cast<const T*>(hidden), sorted, expert_ids, npp, aq1, as1, total, cpr, H, (int)numel, topk, L.cap);
-    if ((rc = check_launch("moe_gather_quant"))) return rc;
+    if (hidden_scale != nullptr)
+      moe_gather_fp8_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
+          static_cast<const uint8_t*>(hidden), hidden_scale, sorted, expert_ids, npp, aq1, as1, total, cpr, H,
+          (int)numel, topk, L.cap);
+    else
+      moe_gather_quant_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
+          static_cast<const T*>(hidden), sorted, expert_ids, npp, aq1, as1, total, cpr, H, (int)numel, topk, L.cap);
+    if ((rc = check_launch("moe_gather"))) return rc;
   }
   int force_bn = 0;
   if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);
@@ -174,7 +202,8 @@ extern "C" size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, in
   return b200::moe_workspace_layout(T, topk, E, H, I).total;
 }
 
-extern "C" int b200_fused_experts_fp8(const void* hidden, int h_dtype, const void* w1, const void* w2,
+extern "C" int b200_fused_experts_fp8(const void* hidden, const float* hidden_scale, int h_dtype, const void* w1,
+                                      const void* w2,
                                       const float* w1_scale, const float* w2_scale, const float* topk_weights,
                                       const int32_t* topk_ids, void* out, int64_t T, int topk, int E, int64_t H,
                                       int64_t I, int no_combine, int apply_router_weight_on_input,
@@ -200,10 +229,10 @@ extern "C" int b200_fused_experts_fp8(const void* hidden, int h_dtype, const voi
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   if (h_dtype == B200_BF16)
-    return run_fused_experts<__nv_bfloat16>(hidden, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T, topk, E,
+    return run_fused_experts<__nv_bfloat16>(hidden, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T, topk, E,
                                             H, I, no_combine, apply_router_weight_on_input, routed_scaling_factor, ws, st);
   if (h_dtype == B200_F16)
-    return run_fused_experts<__half>(hidden, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T, topk, E, H, I,
+    return run_fused_experts<__half>(hidden, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T, topk, E, H, I,
                                      no_combine, apply_router_weight_on_input, routed_scaling_factor, ws, st);
   set_error_detail("fused_experts: hidden dtype code %d is not bf16/f16", h_dtype);
   return B200_E_UNSUPPORTED;

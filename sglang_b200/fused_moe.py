@@ -61,14 +61,29 @@ def fused_experts_impl(
     no_combine: bool = False,
     apply_router_weight_on_input: bool = False,
     routed_scaling_factor: Optional[float] = None,
+    hidden_states_scale: Optional[torch.Tensor] = None,
+    output_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
-    """Checks of the reference's ``fused_experts_impl`` (fused_moe.py:824-834) + the launch."""
+    """Checks of the reference's ``fused_experts_impl`` (fused_moe.py:824-834) + the launch.
+
+    ``hidden_states_scale`` (extension used by the expert-parallel all-to-all path): when given,
+    ``hidden_states`` is already FP8 E4M3 ``[T, H]`` with row-major fp32 1x128 scales
+    ``[T, H/128]`` and ``output_dtype`` names the result dtype."""
     assert hidden_states.shape[1] == w1.shape[2], "Hidden size mismatch"
     assert topk_weights.shape == topk_ids.shape, "topk shape mismatch"
     assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
     assert w1.is_contiguous(), "Expert weights1 must be contiguous"
     assert w2.is_contiguous(), "Expert weights2 must be contiguous"
-    assert hidden_states.dtype in [torch.float16, torch.bfloat16]
+    if hidden_states_scale is None:
+        assert hidden_states.dtype in [torch.float16, torch.bfloat16]
+        out_dtype = hidden_states.dtype
+    else:
+        assert hidden_states.dtype == fp8_dtype and not inplace, "pre-quantised input is FP8 and out of place"
+        assert output_dtype in (torch.float16, torch.bfloat16), "output_dtype must be given for FP8 input"
+        assert tuple(hidden_states_scale.shape) == (hidden_states.shape[0], hidden_states.shape[1] // 128)
+        hidden_states_scale = hidden_states_scale.to(torch.float32).contiguous()
+        N.require_cuda(hidden_states_scale)
+        out_dtype = output_dtype
     assert w1.dtype == fp8_dtype and w2.dtype == fp8_dtype, "expert weights must be float8_e4m3fn"
     assert not (inplace and no_combine), "no combine + inplace makes no sense"
     N.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale)
@@ -88,9 +103,9 @@ def fused_experts_impl(
     if inplace:
         out = hidden_states
     elif no_combine:
-        out = torch.empty((T, topk, H), dtype=hidden_states.dtype, device=hidden_states.device)
+        out = torch.empty((T, topk, H), dtype=out_dtype, device=hidden_states.device)
     else:
-        out = torch.empty_like(hidden_states)
+        out = torch.empty((T, H), dtype=out_dtype, device=hidden_states.device)
     if T == 0:
         return out
     lib = N.load()
@@ -98,7 +113,7 @@ def fused_experts_impl(
     with torch.cuda.device(hidden_states.device):
         ws = _workspace(hidden_states.device, ws_bytes)
         st = lib.b200_fused_experts_fp8(
-            N.ptr(hidden_states), N.DTYPE_CODE[hidden_states.dtype], N.ptr(w1), N.ptr(w2), N.ptr(w1_scale),
+            N.ptr(hidden_states), N.ptr(hidden_states_scale), N.DTYPE_CODE[out_dtype], N.ptr(w1), N.ptr(w2), N.ptr(w1_scale),
             N.ptr(w2_scale), N.ptr(topk_weights), N.ptr(topk_ids), N.ptr(out), T, topk, E, H, I, int(no_combine),
             int(apply_router_weight_on_input),
             1.0 if routed_scaling_factor is None else float(routed_scaling_factor), N.ptr(ws), ws_bytes,
