@@ -4,16 +4,42 @@
 
 #include "gemm_host.cuh"
 
+namespace b200 {
+
+// C[m, n] = sum over splits of the fp32 partials; 8 elements per thread.
+template <typename OutT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C,
+                                                            int64_t mn, int splits) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= mn) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < splits; ++s) {
+    const float4 a = *reinterpret_cast<const float4*>(partial + (int64_t)s * mn + i);
+    const float4 b = *reinterpret_cast<const float4*>(partial + (int64_t)s * mn + i + 4);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  store8<OutT>(C + i, acc);
+}
+
+template <typename OutT>
+static int launch_reduce(const float* partial, void* C, int64_t mn, int splits, cudaStream_t st) {
+  splitk_reduce_kernel<OutT><<<(unsigned)cdiv(mn, 8 * 256), 256, 0, st>>>(partial, static_cast<OutT*>(C), mn, splits);
+  return check_launch("splitk_reduce_kernel");
+}
+
+}  // namespace b200
+
 extern "C" size_t b200_w8a8_block_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  (void)M; (void)N; (void)K;
-  return 0;  // accumulators live in registers / TMEM; no global scratch
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int s = b200::choose_k_splits(M, N, K, 148);  // sized for the largest split any SM count <= 148 picks
+  return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
 
 extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m, int64_t as_stride_k,
                                         const void* B, const float* Bs, void* C, int c_dtype, int64_t M, int64_t N,
                                         int64_t K, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace b200;
-  (void)workspace; (void)workspace_bytes;
   B200_CHECK_ARG(M >= 0 && N >= 0 && K >= 0, "gemm: negative shape");
   if (M == 0 || N == 0) return B200_OK;
   B200_CHECK_ARG(K > 0, "gemm: K must be positive");
@@ -30,6 +56,27 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
   int force_bn = 0;
   if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);  // test hook: 128 or 256
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_CHECK_ARG(c_dtype == B200_BF16 || c_dtype == B200_F16 || c_dtype == B200_F32, "gemm: unknown output dtype code %d",
+                 c_dtype);
+  int splits = choose_k_splits(M, N, K, sm_count() < 148 ? sm_count() : 148);
+  if (const char* e = getenv("B200_GEMM_SPLITK")) splits = atoi(e) > 0 ? atoi(e) : splits;  // test hook
+  if (splits > (int)cdiv(K, 128)) splits = (int)cdiv(K, 128);
+  if (splits > 1) {
+    // decode-sized problem: fp32 partials per K split in the workspace, then one reduction pass
+    const size_t need = (size_t)splits * (size_t)M * (size_t)N * sizeof(float);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) != 0) {
+      set_error_detail("gemm: split-K needs a 16-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
+      return B200_E_WORKSPACE;
+    }
+    p.C = workspace;
+    p.split_stride = M * N;
+    int rc = launch_gemm<GEMM_DENSE, float>(A, B, N, p, 128, st, 0, splits);
+    if (rc) return rc;
+    const float* part = static_cast<const float*>(workspace);
+    if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st);
+    if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st);
+    return launch_reduce<float>(part, C, M * N, splits, st);
+  }
   switch (c_dtype) {
     case B200_BF16: return launch_gemm<GEMM_DENSE, __nv_bfloat16>(A, B, N, p, force_bn, st);
     case B200_F16: return launch_gemm<GEMM_DENSE, __half>(A, B, N, p, force_bn, st);

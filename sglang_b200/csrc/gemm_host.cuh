@@ -6,6 +6,18 @@
 
 namespace b200 {
 
+// Split-K factor for the dense GEMM: when 128 x 128 tiles alone would leave most SMs idle
+// (decode-sized M), split K so that about one work item per SM streams the weights.
+inline int choose_k_splits(int64_t M, int64_t N, int64_t K, int sms) {
+  const int64_t tiles = cdiv(M, 128) * cdiv(N, 128);
+  const int64_t num_kb = cdiv(K, 128);
+  if (tiles * 4 >= (int64_t)sms * 3 || num_kb < 8) return 1;
+  int64_t s = sms / tiles;
+  if (s > num_kb / 4) s = num_kb / 4;
+  if (s > 8) s = 8;
+  return s < 1 ? 1 : (int)s;
+}
+
 // cuTensorMapEncodeTiled, resolved through the runtime so the library needs no -lcuda.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -78,7 +90,7 @@ inline int launch_gemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const 
 // m_tiles_hint: expected number of live 128-row tiles when that is decided on the device.
 template <int MODE, typename OutT>
 inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmParams p, int force_bn,
-                       cudaStream_t st, int64_t m_tiles_hint = 0) {
+                       cudaStream_t st, int64_t m_tiles_hint = 0, int k_splits = 1) {
   p.num_kb = (int)cdiv(p.K, kBK);
   p.n_blocks = (int)cdiv(p.N, 128);
   p.m_tiles = (int)cdiv(p.M, kBM);
@@ -97,7 +109,9 @@ inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmP
   if (force_bn == 128 || force_bn == 256) bn = force_bn;
   p.n_tiles = MODE == GEMM_GROUPED_SILU_QUANT ? p.N / 128 : (int)cdiv(p.N, bn);
   p.group_m = 16;
-  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  p.k_splits = k_splits < 1 ? 1 : k_splits;
+  p.kb_per_split = (int)cdiv(p.num_kb, p.k_splits);
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
   if (tiles == 0) return B200_OK;
   const int grid = (int)(tiles < sms ? tiles : sms);
   CUtensorMap ta, tb;

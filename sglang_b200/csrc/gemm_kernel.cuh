@@ -41,6 +41,10 @@ struct GemmParams {
   int n_tiles;     // ceil(N/BN)
   int m_tiles;     // ceil(M/128) (grouped: upper bound; the live count is read on device)
   int group_m;     // tiles of M swept together for L2 reuse
+  // split-K (dense, small problems): work item = (tile, split); split s covers K blocks
+  // [s*kb_per_split, ...) and writes an fp32 partial at C + s*split_stride
+  int k_splits, kb_per_split;
+  int64_t split_stride;
   // grouped modes
   const int32_t* expert_ids;    // [m_tiles] expert of every 128-row block, -1 = skip
   const int32_t* num_post_pad;  // [1] live rows (multiple of 128)
@@ -66,8 +70,8 @@ struct GemmCfg {
   static constexpr int kStageB = BN * kBK;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
-  // one CTA per SM: 65536 registers / threads, rounded down to the allocation unit of 8
-  static constexpr int kMaxRegs = BN == 256 ? 200 : 255;
+  // Register budget: the register file is split over the four SM sub-partitions (16 K each);
+  // with 10 warps one of them hosts three, so a thread gets at most 168 registers.
   static constexpr int kExchangeBytes = 64 * kBM * 4;  // MODE 1: 64 columns x 128 rows of fp32
   static constexpr size_t smem_bytes(int mode) {
     return (size_t)kStages * (kStageA + kStageB) + (mode == 1 ? kExchangeBytes : 0) + 1024 /*align slack*/ +
@@ -136,7 +140,7 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 }
 
 template <int BN, int MODE, typename OutT>
-__global__ void __maxnreg__(GemmCfg<BN>::kMaxRegs)
+__global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
 block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -189,14 +193,17 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   // live problem size (grouped: decided on the device by the align kernel)
   int m_tiles = p.m_tiles;
   if (MODE != GEMM_DENSE) m_tiles = min(m_tiles, *p.num_post_pad / kBM);
-  const int total_tiles = m_tiles * p.n_tiles;
+  const int S_k = p.k_splits;
+  const int total_items = m_tiles * p.n_tiles * S_k;
   const int num_kb = p.num_kb;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int t = item / S_k, ks = item - t * S_k;
+      const int kb0 = ks * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
       int mt, nt;
       tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
       int b_row = nt * BN, b_row2 = 0;
@@ -210,7 +217,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           b_row += e * p.N;
         }
       }
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % S;
         ok = ptx::mbar_wait(empty_bar(s), ((it / S) & 1) ^ 1, abort_flag);
         if (!ok) break;
@@ -229,11 +236,13 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     constexpr uint32_t idesc = ptx::idesc_e4m3_f32(kBM, BN);
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int t = item / S_k, ks = item - t * S_k;
+      const int kb0 = ks * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
       int mt, nt;
       tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
       if (MODE != GEMM_DENSE && p.expert_ids[mt] < 0) continue;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % S, b = it & 1;
         ok = ptx::mbar_wait(tempty_bar(b), ((it >> 1) & 1) ^ 1, abort_flag) &&
              ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag);
@@ -245,7 +254,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint32_t d = tmem_base + b * BN;
 #pragma unroll
           for (int k = 0; k < kBK / 32; ++k)  // +32 bytes along K inside the swizzle row = +2 in the address field
-            ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, k > 0);
+            ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, k > 0);  // k == 0 overwrites the buffer
           ptx::mma_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
           ptx::mma_commit(tfull_bar(b));   // partial product ready for the promotion warps
         }
@@ -259,7 +268,9 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int t = item / S_k, ks = item - t * S_k;
+      const int kb0 = ks * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
       int mt, nt;
       tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
       int expert = 0;
@@ -285,12 +296,12 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       float a_pf[4], b_pf[4];
 #pragma unroll
       for (int d = 0; d < 4; ++d) {
-        const bool in = row_ok && d < num_kb;
-        a_pf[d] = in ? __ldg(as_ptr + (int64_t)d * p.as_sk) : 0.f;
-        b_pf[d] = in ? __ldg(bs_ptr + d) : 0.f;
+        const bool in = row_ok && kb0 + d < kb1;
+        a_pf[d] = in ? __ldg(as_ptr + (int64_t)(kb0 + d) * p.as_sk) : 0.f;
+        b_pf[d] = in ? __ldg(bs_ptr + kb0 + d) : 0.f;
       }
 
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int b = it & 1;
         const float sc = a_pf[0] * b_pf[0];
         const float2 sc2 = make_float2(sc, sc);
@@ -300,7 +311,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           b_pf[d] = b_pf[d + 1];
         }
         {
-          const bool in = row_ok && kb + 4 < num_kb;
+          const bool in = row_ok && kb + 4 < kb1;
           a_pf[3] = in ? __ldg(as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
           b_pf[3] = in ? __ldg(bs_ptr + kb + 4) : 0.f;
         }
@@ -390,7 +401,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
       }
       if (store) {
-        OutT* dst = static_cast<OutT*>(p.C) + out_row * p.ldc + col0;
+        OutT* dst = static_cast<OutT*>(p.C) + ks * p.split_stride + out_row * p.ldc + col0;
 #pragma unroll
         for (int j = 0; j < 16; ++j)
           if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, acc + j * 8);

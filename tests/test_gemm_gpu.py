@@ -24,7 +24,7 @@ def _rand_fp8(shape, seed):
     return ((torch.rand(shape, generator=g) - 0.5) * 2 * 448).clamp(-448, 448).to(torch.float8_e4m3fn)
 
 
-def _case(M, N, K, seed, out_dtype=torch.bfloat16, col_major=False, bn=None):
+def _case(M, N, K, seed, out_dtype=torch.bfloat16, col_major=False, bn=None, splitk=None):
     import sglang_b200 as S
 
     g = torch.Generator().manual_seed(seed)
@@ -39,11 +39,14 @@ def _case(M, N, K, seed, out_dtype=torch.bfloat16, col_major=False, bn=None):
         assert As_d.stride() == (1, M)
     if bn:
         os.environ["B200_GEMM_BN"] = str(bn)
+    if splitk:
+        os.environ["B200_GEMM_SPLITK"] = str(splitk)
     try:
         C = S.w8a8_block_fp8_matmul(A.cuda(), B.cuda(), As_d, Bs.cuda(), [128, 128], out_dtype)
         _status_ok()
     finally:
         os.environ.pop("B200_GEMM_BN", None)
+        os.environ.pop("B200_GEMM_SPLITK", None)
     assert C.dtype == out_dtype and tuple(C.shape) == (M, N)
     err = O.rel_frobenius(C.float().cpu(), ref)
     assert err < (1e-5 if out_dtype == torch.float32 else TOL), (M, N, K, err)
@@ -75,6 +78,14 @@ def test_shapes_both_tile_widths(M, N, K, bn):
 def test_output_dtypes_and_column_major_scales(dtype):
     _case(83, 512, 512, 5, out_dtype=dtype)
     _case(83, 512, 512, 6, out_dtype=dtype, col_major=True)
+
+
+@pytest.mark.parametrize("splitk", [2, 3, 8])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 1024), (16, 384, 2048), (130, 256, 1152), (64, 128, 896)])
+def test_split_k(M, N, K, splitk):
+    # K blocks that do not divide evenly over the splits, ragged M, fp32 partials + reduction
+    _case(M, N, K, 300 + M + splitk, splitk=splitk)
+    _case(M, N, K, 301 + M + splitk, splitk=splitk, out_dtype=torch.float32)
 
 
 def test_many_tiles_persistent_loop():
