@@ -101,6 +101,26 @@ int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel
                               void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * moe_align_block_size without a workspace (no counterpart in the reference).
+ * For callers that cannot allocate device memory at the point of the call -- a host that may
+ * not call cudaMalloc (e.g. inside a region where the allocator is frozen, or an embedding
+ * runtime that owns all device memory) and therefore has no workspace to hand over. Same
+ * inputs, outputs and results as b200_moe_align_block_size; the scratch of the multi-block path
+ * is a fixed array inside the library (about 129 KB of device memory held by every GPU that
+ * loads the library, until the process exits). Limits: numel <= 131072 ids and
+ * num_buckets <= 257; anything larger returns B200_E_UNSUPPORTED.
+ * The first call on each device resolves the array's device address (one runtime query, no
+ * allocation): make that first call before starting any stream capture. The call itself
+ * allocates nothing. All calls on a device share the one array: two calls whose kernels can
+ * overlap on the GPU (different streams) race on it -- keep them on one stream or order them
+ * with events. The array needs no clearing between calls: every word a call reads, it wrote
+ * earlier in the same call. */
+int b200_moe_align_block_size_static(const void* topk_ids, int ids_dtype, int64_t numel,
+                                     int num_buckets, int block_size, int32_t* sorted_token_ids,
+                                     int64_t max_pad, int32_t* expert_ids, int64_t max_blocks,
+                                     int32_t* num_post_pad, int32_t* cumsum, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * fused_experts(use_fp8_w8a8=True, block_shape=[128,128])
  * replaces: python/sglang/srt/layers/moe/moe_runner/triton_utils/fused_moe.py:218-306
  *           (kernel sequence :401-785: align -> quant -> grouped GEMM -> silu_and_mul ->

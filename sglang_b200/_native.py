@@ -37,6 +37,10 @@ SIGNATURES = {
         [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int,
          c_void_p, c_size_t, c_void_p],
     ),
+    "b200_moe_align_block_size_static": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
+    ),
     "b200_fused_experts_fp8_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int64, c_int64]),
     "b200_fused_experts_fp8": (
         c_int,

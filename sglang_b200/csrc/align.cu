@@ -212,6 +212,37 @@ static int launch_align(const void* ids_, int64_t numel, int B, int block_size, 
   return check_launch("moe_align_block_size");
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for callers that must not allocate device memory: the per-chunk histograms of the
+// multi-block path live in this fixed array instead of a caller-provided workspace. Every
+// device that loads the library carries the array (about 129 KB) until the process exits.
+constexpr int64_t kStaticAlignMaxNumel = 131072;  // e.g. 16384 tokens x top-8
+constexpr int kStaticAlignMaxBuckets = 257;       // 256 experts + the "-1" bucket
+static __device__ __align__(256) int32_t g_align_static_scratch[(kStaticAlignMaxNumel / kAlignThreads) *
+                                                                kStaticAlignMaxBuckets];
+
+// Device address of the array on the CURRENT device. The symbol name is only a host-side
+// handle; a kernel must be given the address cudaGetSymbolAddress reports for that device.
+static int32_t* align_static_scratch_ptr() {
+  constexpr int kMaxDevices = 64;
+  static int32_t* cache[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error_detail("align (static scratch): cannot identify the current device");
+    return nullptr;
+  }
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_align_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error_detail("align (static scratch): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cache[dev] = static_cast<int32_t*>(p);  // same value from any thread: a benign race
+  }
+  return cache[dev];
+}
+
 }  // namespace b200
 
 extern "C" size_t b200_moe_align_workspace_bytes(int64_t numel, int num_buckets) {
@@ -249,4 +280,23 @@ extern "C" int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, in
                                  max_blocks, num_post_pad, cumsum, workspace, st);
   set_error_detail("align: ids dtype code %d is not int32/int64", ids_dtype);
   return B200_E_BAD_ARG;
+}
+
+extern "C" int b200_moe_align_block_size_static(const void* topk_ids, int ids_dtype, int64_t numel, int num_buckets,
+                                                int block_size, int32_t* sorted_token_ids, int64_t max_pad,
+                                                int32_t* expert_ids, int64_t max_blocks, int32_t* num_post_pad,
+                                                int32_t* cumsum, void* stream) {
+  using namespace b200;
+  if (numel > kStaticAlignMaxNumel || num_buckets > kStaticAlignMaxBuckets) {
+    set_error_detail("align (static scratch): numel=%lld / num_buckets=%d exceed the built-in limits of %lld ids and "
+                     "%d buckets; use b200_moe_align_block_size with a workspace",
+                     (long long)numel, num_buckets, (long long)kStaticAlignMaxNumel, kStaticAlignMaxBuckets);
+    return B200_E_UNSUPPORTED;
+  }
+  int32_t* scratch = align_static_scratch_ptr();
+  if (scratch == nullptr) return B200_E_LAUNCH;
+  return b200_moe_align_block_size(topk_ids, ids_dtype, numel, num_buckets, block_size, sorted_token_ids, max_pad,
+                                   expert_ids, max_blocks, num_post_pad, cumsum, 1, scratch,
+                                   sizeof(int32_t) * (size_t)(kStaticAlignMaxNumel / kAlignThreads) * kStaticAlignMaxBuckets,
+                                   stream);
 }
