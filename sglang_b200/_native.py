@@ -13,7 +13,8 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "_lib", "libb200_blockfp8.so")
+# SGLANG_B200_LIB points at another build of the same library (e.g. one compiled with tuning macros)
+LIB_PATH = os.environ.get("SGLANG_B200_LIB") or os.path.join(_PKG, "_lib", "libb200_blockfp8.so")
 
 # Every symbol the header declares: name -> (restype, argtypes)
 SIGNATURES = {
@@ -113,7 +114,38 @@ def ptr(t) -> int:
 
 
 def current_stream(device=None) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Raw cudaStream_t of torch's current stream on ``device`` (default: current device)."""
+    if device is None:
+        idx = torch.cuda.current_device()
+    else:
+        idx = device.index if isinstance(device, torch.device) else int(device)
+        if idx is None:
+            idx = torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(idx)
+
+
+class on_device:
+    """``with on_device(t):`` makes ``t``'s device current for the duration of a launch; a no-op
+    (and allocation-free) when it already is, which is the case on every call of a
+    one-process-per-GPU server."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, t: torch.Tensor):
+        self.idx = t.device.index
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and self.idx != cur:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *a):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def read_device_status() -> int:

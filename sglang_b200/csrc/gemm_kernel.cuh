@@ -65,13 +65,19 @@ constexpr int kBK = 128;  // bytes == elements (fp8) == one scale block == one s
 template <int BN>
 struct GemmCfg {
   static constexpr int kEpiWarps = BN / 32;  // 4 or 8: warp e -> TMEM lanes 32*(e%4), columns 128*(e/4)
-  static constexpr int kThreads = (kEpiWarps + 2) * 32;
+  // BN = 256 runs three full warpgroups (8 promotion warps; producer, MMA issuer and two idle
+  // warps) so that registers can be moved between warpgroups with setmaxnreg.
+  static constexpr int kThreads = BN == 256 ? 384 : (kEpiWarps + 2) * 32;
+  static constexpr bool kRebalanceRegs = BN == 256;
+  static constexpr int kRegsPromotion = 224, kRegsOther = 56;  // 256*224 + 128*56 = 64512 <= 65536
   static constexpr int kStageA = kBM * kBK;
   static constexpr int kStageB = BN * kBK;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
-  // Register budget: the register file is split over the four SM sub-partitions (16 K each);
-  // with 10 warps one of them hosts three, so a thread gets at most 168 registers.
+  // Register budget: the register file is split over the four SM sub-partitions (16 K each).
+  // 12 warps start with 168 registers each (3 warps per sub-partition); the promotion warps,
+  // which hold 128 accumulators + 64 staged TMEM values, then grow to 224 with setmaxnreg
+  // while the producer / MMA warpgroup shrinks to 56 (2*224 + 56 = 504 <= 512 per sub-partition).
   static constexpr int kExchangeBytes = 64 * kBM * 4;  // MODE 1: 64 columns x 128 rows of fp32
   static constexpr size_t smem_bytes(int mode) {
     return (size_t)kStages * (kStageA + kStageB) + (mode == 1 ? kExchangeBytes : 0) + 1024 /*align slack*/ +
@@ -116,15 +122,11 @@ __device__ __forceinline__ void store8<float>(float* dst, const float* a) {
   *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
 }
 
-// acc[0..32) += v[0..32) * scale, two lanes of fp32 per instruction (packed FFMA2 on sm_100).
-__device__ __forceinline__ void promote32(float* acc, const uint32_t (&v)[32], float2 sc2) {
+// acc[0..32) += v[0..32) * scale. (The packed fma.f32x2 form was measured slower here: the
+// staged TMEM registers do not come out as aligned pairs.)
+__device__ __forceinline__ void promote32(float* acc, const uint32_t (&v)[32], float sc) {
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const float2 r = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), sc2,
-                                make_float2(acc[2 * j], acc[2 * j + 1]));
-    acc[2 * j] = r.x;
-    acc[2 * j + 1] = r.y;
-  }
+  for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v[j]), sc, acc[j]);
 }
 
 // tile index -> (m_tile, n_tile): sweep group_m row-tiles for every column tile before moving
@@ -197,6 +199,9 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int total_items = m_tiles * p.n_tiles * S_k;
   const int num_kb = p.num_kb;
 
+  if (warp >= Cfg::kEpiWarps) {
+  // the producer / MMA warpgroup hands registers to the promotion warpgroups
+  if constexpr (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::kRegsOther));
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t it = 0;
@@ -261,84 +266,111 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         __syncwarp();
       }
     }
+  }
   } else {
     // ------------------------------------------------------------- promotion warps
+    if constexpr (Cfg::kRebalanceRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::kRegsPromotion));
     const int quarter = warp & 3, half = warp >> 2;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
+
+    // Everything a work item needs, including its first four scale pairs already in flight.
+    // The context of item i+1 is set up BEFORE the epilogue of item i, so the L2 round trips
+    // of its scales (and of its expert id) overlap the stores instead of stalling the MMA.
+    struct Item {
+      int item, mt, nt, ks, kb0, kb1, expert, row, col0;
+      bool row_ok;
+      const float* as_ptr;
+      const float* bs_ptr;
+      float a_pf[4], b_pf[4];
+    };
+    auto setup = [&](int item, Item& c) -> bool {
+      for (; item < total_items; item += gridDim.x) {
+        const int t = item / S_k;
+        c.ks = item - t * S_k;
+        c.kb0 = c.ks * p.kb_per_split;
+        c.kb1 = min(num_kb, c.kb0 + p.kb_per_split);
+        tile_coords(t, m_tiles, p.n_tiles, p.group_m, c.mt, c.nt);
+        c.expert = 0;
+        if (MODE != GEMM_DENSE) {
+          c.expert = p.expert_ids[c.mt];
+          if (c.expert < 0) continue;  // rows of experts that live on another rank
+        }
+        c.item = item;
+        c.row = c.mt * kBM + row_in_tile;
+        c.col0 = MODE == GEMM_GROUPED_SILU_QUANT ? c.nt * 128 : c.nt * BN + half * 128;
+        c.row_ok = c.row < p.M;
+        c.as_ptr = p.As + (int64_t)(c.row_ok ? c.row : 0) * p.as_sm;
+        // row of Bs: the 128-row block of B this thread's columns come from (MODE 1: gate block
+        // nt for the first 128 TMEM columns, up block I/128 + nt for the other 128)
+        const int nb = MODE == GEMM_GROUPED_SILU_QUANT ? half * p.n_blocks + c.nt : min(c.col0 / 128, p.n_blocks - 1);
+        const int bs_rows = MODE == GEMM_GROUPED_SILU_QUANT ? 2 * p.n_blocks : p.n_blocks;
+        c.bs_ptr = p.Bs + ((int64_t)c.expert * bs_rows + nb) * num_kb;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          const bool in = c.row_ok && c.kb0 + d < c.kb1;
+          c.a_pf[d] = in ? __ldg(c.as_ptr + (int64_t)(c.kb0 + d) * p.as_sk) : 0.f;
+          c.b_pf[d] = in ? __ldg(c.bs_ptr + c.kb0 + d) : 0.f;
+        }
+        return true;
+      }
+      return false;
+    };
+
     uint32_t it = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const int t = item / S_k, ks = item - t * S_k;
-      const int kb0 = ks * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
-      int mt, nt;
-      tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
-      int expert = 0;
-      if (MODE != GEMM_DENSE) {
-        expert = p.expert_ids[mt];
-        if (expert < 0) continue;
-      }
-      const int row = mt * kBM + row_in_tile;
-      const int col0 = MODE == GEMM_GROUPED_SILU_QUANT ? nt * 128 : nt * BN + half * 128;
-      const bool row_ok = row < p.M;
-      const float* as_ptr = p.As + (int64_t)(row_ok ? row : 0) * p.as_sm;
-      // row of Bs: 128-row block of B this thread's columns come from (MODE 1: gate block nt
-      // for the first 128 TMEM columns, up block I/128 + nt for the other 128)
-      const int nb = MODE == GEMM_GROUPED_SILU_QUANT ? half * p.n_blocks + nt : min(col0 / 128, p.n_blocks - 1);
-      const int bs_rows = MODE == GEMM_GROUPED_SILU_QUANT ? 2 * p.n_blocks : p.n_blocks;
-      const float* bs_ptr = p.Bs + ((int64_t)expert * bs_rows + nb) * num_kb;
-
+    Item cur;
+    bool have = setup(blockIdx.x, cur);
+    while (have) {
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      // Scales are fetched four K blocks ahead (an L2 round trip is longer than one K block of
-      // MMA) and multiplied only when used, so no iteration waits on a load it just issued.
-      float a_pf[4], b_pf[4];
-#pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const bool in = row_ok && kb0 + d < kb1;
-        a_pf[d] = in ? __ldg(as_ptr + (int64_t)(kb0 + d) * p.as_sk) : 0.f;
-        b_pf[d] = in ? __ldg(bs_ptr + kb0 + d) : 0.f;
-      }
 
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      for (int kb = cur.kb0; kb < cur.kb1; ++kb, ++it) {
         const int b = it & 1;
-        const float sc = a_pf[0] * b_pf[0];
-        const float2 sc2 = make_float2(sc, sc);
+        // scales are multiplied only when used, four K blocks after their loads were issued
+        const float sc = cur.a_pf[0] * cur.b_pf[0];
 #pragma unroll
         for (int d = 0; d < 3; ++d) {
-          a_pf[d] = a_pf[d + 1];
-          b_pf[d] = b_pf[d + 1];
+          cur.a_pf[d] = cur.a_pf[d + 1];
+          cur.b_pf[d] = cur.b_pf[d + 1];
         }
         {
-          const bool in = row_ok && kb + 4 < kb1;
-          a_pf[3] = in ? __ldg(as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
-          b_pf[3] = in ? __ldg(bs_ptr + kb + 4) : 0.f;
+          const bool in = cur.row_ok && kb + 4 < cur.kb1;
+          cur.a_pf[3] = in ? __ldg(cur.as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
+          cur.b_pf[3] = in ? __ldg(cur.bs_ptr + kb + 4) : 0.f;
         }
         ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
         if (!ok) break;
         ptx::tc_fence_after();
         const uint32_t ta = lane_base + b * BN;
         uint32_t va[32], vb[32];
-        // two TMEM loads in flight per wait; the second pair overlaps the FMAs of the first
+        // one TMEM load in flight behind the FMAs of the previous 32 columns
         ptx::tmem_ld32(ta, va);
+        ptx::tmem_ld_wait(va);
         ptx::tmem_ld32(ta + 32, vb);
-        ptx::tmem_ld_wait2(va, vb);
-        promote32(acc, va, sc2);
+        promote32(acc, va, sc);
+        ptx::tmem_ld_wait(vb);
         ptx::tmem_ld32(ta + 64, va);
-        promote32(acc + 32, vb, sc2);
+        promote32(acc + 32, vb, sc);
+        ptx::tmem_ld_wait(va);
         ptx::tmem_ld32(ta + 96, vb);
-        ptx::tmem_ld_wait2(va, vb);
+        promote32(acc + 64, va, sc);
+        ptx::tmem_ld_wait(vb);
         // every TMEM read of this buffer has landed: give it back to the MMA warp
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-        promote32(acc + 64, va, sc2);
-        promote32(acc + 96, vb, sc2);
+        promote32(acc + 96, vb, sc);
       }
       if (!ok) break;
 
+      Item nxt;
+      const bool have_next = setup(cur.item + gridDim.x, nxt);
+
       // ------------------------------------------------------------ tile epilogue
+      const int row = cur.row, col0 = cur.col0, nt = cur.nt, ks = cur.ks;
+      const bool row_ok = cur.row_ok;
       if (MODE == GEMM_GROUPED_SILU_QUANT) {
         if (p.topk_weights != nullptr) {
           // router weight applied to the gate_up product in fp32, before the activation (where
@@ -386,26 +418,28 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           p.q_scales[(int64_t)nt * p.q_scale_ld + row] = __fdiv_rn(amax, 448.0f);
         }
-        continue;
-      }
-      int64_t out_row = row;
-      bool store = row_ok;
-      if (MODE == GEMM_GROUPED_SCATTER) {
-        const int flat = store ? p.sorted_ids[row] : p.numel;
-        store = store && flat < p.numel;
-        out_row = flat;
-        if (store && p.topk_weights != nullptr) {
-          const float w = __ldg(p.topk_weights + flat);
+      } else {
+        int64_t out_row = row;
+        bool store = row_ok;
+        if (MODE == GEMM_GROUPED_SCATTER) {
+          const int flat = store ? p.sorted_ids[row] : p.numel;
+          store = store && flat < p.numel;
+          out_row = flat;
+          if (store && p.topk_weights != nullptr) {
+            const float w = __ldg(p.topk_weights + flat);
 #pragma unroll
-          for (int j = 0; j < 128; ++j) acc[j] *= w;
+            for (int j = 0; j < 128; ++j) acc[j] *= w;
+          }
+        }
+        if (store) {
+          OutT* dst = static_cast<OutT*>(p.C) + ks * p.split_stride + out_row * p.ldc + col0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, acc + j * 8);
         }
       }
-      if (store) {
-        OutT* dst = static_cast<OutT*>(p.C) + ks * p.split_stride + out_row * p.ldc + col0;
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, acc + j * 8);
-      }
+      cur = nxt;
+      have = have_next;
     }
   }
 

@@ -93,7 +93,7 @@ def per_token_group_quant_fp8(
             sm, sg = x_s.stride(0), x_s.stride(1)
         else:
             sm, sg = K // group_size, 1
-        with torch.cuda.device(x.device):
+        with N.on_device(x):
             st = N.load().b200_per_token_group_quant_fp8(
                 N.ptr(x), N.DTYPE_CODE[x.dtype], N.ptr(x_q), N.ptr(x_s), M, K, group_size, sm, sg, eps,
                 _QUANT_FORMULA, N.current_stream(),
@@ -132,7 +132,7 @@ def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
     """Grow-only per-(device, stream) scratch buffer for the kernels that need one."""
     if nbytes == 0:
         return None
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, N.current_stream(device))
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -170,7 +170,7 @@ def w8a8_block_fp8_matmul(
     ws_bytes = lib.b200_w8a8_block_fp8_gemm_workspace_bytes(M, Nn, K)
     if "B200_GEMM_SPLITK" in os.environ:  # test hook of the native side: size for the forced split
         ws_bytes = max(ws_bytes, int(os.environ["B200_GEMM_SPLITK"]) * M * Nn * 4)
-    with torch.cuda.device(A.device):
+    with N.on_device(A):
         ws = _workspace(A.device, ws_bytes)
         st = lib.b200_w8a8_block_fp8_gemm(
             N.ptr(A), N.ptr(As2), As2.stride(0), As2.stride(1), N.ptr(B), N.ptr(Bs), N.ptr(C),

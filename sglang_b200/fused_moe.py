@@ -110,7 +110,7 @@ def fused_experts_impl(
         return out
     lib = N.load()
     ws_bytes = lib.b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I)
-    with torch.cuda.device(hidden_states.device):
+    with N.on_device(hidden_states):
         ws = _workspace(hidden_states.device, ws_bytes)
         st = lib.b200_fused_experts_fp8(
             N.ptr(hidden_states), N.ptr(hidden_states_scale), N.DTYPE_CODE[out_dtype], N.ptr(w1), N.ptr(w2), N.ptr(w1_scale),

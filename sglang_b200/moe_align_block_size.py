@@ -40,7 +40,7 @@ def sgl_moe_align_block_size(
     lib = N.load()
     numel = topk_ids.numel()
     ws_bytes = lib.b200_moe_align_workspace_bytes(numel, num_experts)
-    with torch.cuda.device(topk_ids.device):
+    with N.on_device(topk_ids):
         ws = _workspace(topk_ids.device, ws_bytes)
         st = lib.b200_moe_align_block_size(
             N.ptr(topk_ids), N.DTYPE_CODE[topk_ids.dtype], numel, num_experts, block_size,
