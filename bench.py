@@ -36,6 +36,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+if "reference" in sys.argv and os.environ.get("OMP_NUM_THREADS") == "1":
+    # torchrun pins OMP_NUM_THREADS=1 for its ranks; the CPU arm is meant to use every host thread
+    del os.environ["OMP_NUM_THREADS"]
 
 import torch  # noqa: E402
 
@@ -249,6 +252,78 @@ def bench_moe(S, device, steps: int):
     return out
 
 
+def bench_parallel(S, device, rank: int, world: int, steps: int):
+    """Extra line items at N > 1: Llama-3-70B-shaped tensor-parallel linears (M = 4096; column-parallel
+    qkv + gate_up, row-parallel o_proj + down with the bf16 all-reduce) and the DeepSeek-V3-shaped MoE
+    layer expert-parallel over the N ranks (T = 16384 tokens in total; "standard" = replicated tokens +
+    all-reduce, "a2a" = tokens partitioned + all-to-all dispatch / combine). Device time, max over ranks."""
+    from sglang_b200 import parallel as P
+    from sglang_b200 import synthetic
+    from sglang_b200.topk import biased_grouped_topk
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier(world)
+        return dist_max(e0.elapsed_time(e1) / n, world, device)
+
+    out = {}
+    M = 4096
+    layers, flops = [], 0
+    for i, (name, (n, k, kind)) in enumerate(synthetic.LLAMA3_70B_TP_LINEARS.items()):
+        g = torch.Generator(device=device).manual_seed(3000 + i)
+        # each rank draws only its own shard (same values as slicing a full tensor would need 0.5 GB per layer on every rank)
+        if kind == "column":
+            w = (torch.randn(n // world, k, generator=g, device=device) * 0.02).bfloat16()
+            x = torch.randn(M, k, generator=g, device=device).bfloat16()
+        else:
+            w = (torch.randn(n, k // world, generator=g, device=device) * 0.02).bfloat16()
+            x = torch.randn(M, k // world, generator=g, device=device).bfloat16()
+        wq, ws = synthetic.block_quant_weight_fp8(w)
+        layers.append((kind, x, wq, ws))
+        flops += 2 * M * n * k
+    del w
+
+    def tp_step():
+        for kind, x, wq, ws in layers:
+            y = S.w8a8_block_fp8_linear(x, wq, [128, 128], ws)
+            if kind == "row":
+                P.tensor_model_parallel_all_reduce(y)
+
+    ms = timed(tp_step, steps)
+    out["tp_llama70b_M4096"] = {"tflops": flops / ms / 1e9, "ms": ms, "tp": world,
+                                "allreduce_bytes_per_step": 2 * M * 8192 * 2}
+    del layers
+    torch.cuda.empty_cache()
+
+    cfg = synthetic.DEEPSEEK_V3
+    E, topk, H, I, T = cfg["E"], cfg["topk"], cfg["H"], cfg["I"], 16384
+    el = E // world
+    w1, w2, w1_s, w2_s = synthetic.expert_weights(el, I, H, 4000 + E, device=device, first_expert=rank * el)
+    g = torch.Generator().manual_seed(5000 + T)
+    x = torch.randn(T, H, generator=g).bfloat16().to(device)
+    logits = torch.randn(T, E, generator=g).to(device)
+    tw, ti = biased_grouped_topk(x, logits, torch.zeros(E, device=device), topk, True, cfg["n_group"], cfg["topk_group"])
+    for mode, label in (("ep", "standard"), ("ep_a2a", "a2a")):
+        layer = P.FusedMoE(w1, w2, w1_s, w2_s, rank, world, mode=mode, presharded=True, num_experts=E)
+        if mode == "ep":
+            xs, ws_, is_ = x, tw, ti
+        else:
+            per = T // world
+            sl = slice(rank * per, (rank + 1) * per)
+            xs, ws_, is_ = x[sl].contiguous(), tw[sl].contiguous(), ti[sl].contiguous()
+        ms = timed(lambda: layer(xs, ws_, is_), max(2, steps // 2))
+        out[f"ep_deepseek_v3_T16384_{label}"] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "ep": world,
+                                                 "tflops": 6 * T * topk * H * I / ms / 1e9}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,15 +418,22 @@ def main():
                    "parallelism": f"{world} independent replicas" if world > 1 else "single GPU"},
         "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": args.steps * 2 * len(LINEARS), "roofline": roofline,
     }
+    del acts_dev, outs_host
+    torch.cuda.empty_cache()
+    if world > 1 and not args.no_extras:
+        try:
+            line["parallel"] = bench_parallel(S, device, rank, world, steps=6)
+        except Exception as e:  # the headline number stands without the extra line items
+            line["parallel"] = {"error": repr(e)}
+            barrier(world)
     if rank == 0 and not args.no_extras:
-        del acts_dev, outs_host
-        torch.cuda.empty_cache()
         if world == 1:
             try:
                 line["moe"] = bench_moe(S, device, steps=5)
             except Exception as e:  # the headline number stands without the extra line items
                 line["moe"] = {"error": repr(e)}
-        line["cpu_baseline"] = time_cpu_baseline()
+        if world == 1:
+            line["cpu_baseline"] = time_cpu_baseline()
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

@@ -55,6 +55,7 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   int force_bn = 0;
   if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);  // test hook: 128 or 256
+
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_CHECK_ARG(c_dtype == B200_BF16 || c_dtype == B200_F16 || c_dtype == B200_F32, "gemm: unknown output dtype code %d",
                  c_dtype);

@@ -2,6 +2,8 @@
 // the dense linear entry point and the fused-MoE entry point.
 #pragma once
 
+#include <type_traits>
+
 #include "gemm_kernel.cuh"
 
 namespace b200 {
@@ -59,6 +61,33 @@ inline int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_
   return B200_OK;
 }
 
+// Output tensor [S, rows, cols] (S = K splits, 1 otherwise) of `elem_bytes`-wide elements, stored
+// through boxes of [32 rows x 128 bytes] with the 128-byte swizzle.
+inline int make_tmap_out(CUtensorMap* m, const void* base, uint64_t splits, uint64_t rows, uint64_t cols,
+                         int elem_bytes, bool is_bf16, const char* what) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    set_error_detail("cuTensorMapEncodeTiled is not available from the driver");
+    return B200_E_LAUNCH;
+  }
+  const CUtensorMapDataType dt = elem_bytes == 1   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : is_bf16         ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[3] = {cols, rows, splits};
+  cuuint64_t strides[2] = {cols * (uint64_t)elem_bytes, rows * cols * (uint64_t)elem_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error_detail("cuTensorMapEncodeTiled(%s: splits=%llu rows=%llu cols=%llu elem=%d) failed with CUresult %d", what,
+                     (unsigned long long)splits, (unsigned long long)rows, (unsigned long long)cols, elem_bytes, (int)r);
+    return B200_E_LAUNCH;
+  }
+  return B200_OK;
+}
+
 inline int sm_count() {
   static thread_local int dev_cached = -1, sms = 0;
   int dev = 0;
@@ -71,17 +100,17 @@ inline int sm_count() {
 }
 
 template <int BN, int MODE, typename OutT>
-inline int launch_gemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                            cudaStream_t st) {
+inline int launch_gemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                            int grid, cudaStream_t st) {
   auto k = block_fp8_gemm_kernel<BN, MODE, OutT>;
   // per device and cheap: set on every launch rather than caching per device
-  const size_t smem = GemmCfg<BN>::smem_bytes(MODE);
+  const size_t smem = GemmLayout<BN, MODE, OutT>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error_detail("cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
     return B200_E_LAUNCH;
   }
-  k<<<grid, GemmCfg<BN>::kThreads, smem, st>>>(ta, tb, p);
+  k<<<grid, GemmCfg<BN>::kThreads, smem, st>>>(ta, tb, tc, p);
   return check_launch("block_fp8_gemm_kernel");
 }
 
@@ -120,12 +149,20 @@ inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmP
   rc = make_tmap_u8(&tb, B, (uint64_t)b_rows_total, (uint64_t)p.K,
                     MODE == GEMM_GROUPED_SILU_QUANT ? 128u : (uint32_t)bn, "B");
   if (rc) return rc;
-  if (bn == 256) return launch_gemm_inst<256, MODE, OutT>(ta, tb, p, grid, st);
+  // output map: dense -> C [splits, M, N]; gate_up -> FP8 activation [cap, I]; scatter -> unused
+  CUtensorMap tc = ta;
+  if (MODE == GEMM_DENSE)
+    rc = make_tmap_out(&tc, p.C, (uint64_t)p.k_splits, (uint64_t)p.M, (uint64_t)p.N, (int)sizeof(OutT),
+                       std::is_same<OutT, __nv_bfloat16>::value, "C");
+  else if (MODE == GEMM_GROUPED_SILU_QUANT)
+    rc = make_tmap_out(&tc, p.q_out, 1, (uint64_t)p.M, (uint64_t)p.N, 1, false, "q_out");
+  if (rc) return rc;
+  if (bn == 256) return launch_gemm_inst<256, MODE, OutT>(ta, tb, tc, p, grid, st);
   if constexpr (MODE == GEMM_GROUPED_SILU_QUANT) {
     set_error_detail("gate_up GEMM needs 256-wide tiles");
     return B200_E_BAD_ARG;
   } else {
-    return launch_gemm_inst<128, MODE, OutT>(ta, tb, p, grid, st);
+    return launch_gemm_inst<128, MODE, OutT>(ta, tb, tc, p, grid, st);
   }
 }
 

@@ -72,17 +72,36 @@ struct GemmCfg {
   static constexpr int kRegsPromotion = 224, kRegsOther = 56;  // 256*224 + 128*56 = 64512 <= 65536
   static constexpr int kStageA = kBM * kBK;
   static constexpr int kStageB = BN * kBK;
-  static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
   // Register budget: the register file is split over the four SM sub-partitions (16 K each).
   // 12 warps start with 168 registers each (3 warps per sub-partition); the promotion warps,
   // which hold 128 accumulators + 64 staged TMEM values, then grow to 224 with setmaxnreg
   // while the producer / MMA warpgroup shrinks to 56 (2*224 + 56 = 504 <= 512 per sub-partition).
   static constexpr int kExchangeBytes = 64 * kBM * 4;  // MODE 1: 64 columns x 128 rows of fp32
-  static constexpr size_t smem_bytes(int mode) {
-    return (size_t)kStages * (kStageA + kStageB) + (mode == 1 ? kExchangeBytes : 0) + 1024 /*align slack*/ +
-           256 /*barriers*/;
-  }
+};
+
+// Shared-memory plan of one instantiation. The promotion warps stage their part of the output
+// tile (32 rows x 128 columns per warp) in shared memory in the TMA 128-byte-swizzled box layout
+// and write it out with bulk tensor stores (dense, gate_up) or with row-contiguous 16-byte
+// stores (scatter): a thread owns a whole row, so direct stores would touch 32 different rows
+// per instruction. Staging is used by the 256-wide tile with 16-bit / FP8 output (the shapes
+// where the epilogue is on the critical path); fp32 output and the 128-wide tile (small
+// problems, split-K partials) keep direct row stores.
+template <int BN, int MODE, typename OutT>
+struct GemmLayout {
+  using Cfg = GemmCfg<BN>;
+  static constexpr int kRowBytes = MODE == GEMM_GROUPED_SILU_QUANT ? 128 : 128 * (int)sizeof(OutT);  // per thread
+  static constexpr bool kStaged = BN == 256 && kRowBytes <= 256;
+  static constexpr int kBoxesPerWarp = kRowBytes / 128;     // boxes of 32 rows x 128 bytes
+  static constexpr int kWarpStageBytes = 32 * kRowBytes;    // 4, 8 or 16 KB
+  static constexpr int kStoreWarps = MODE == GEMM_GROUPED_SILU_QUANT ? 4 : Cfg::kEpiWarps;
+  static constexpr int kStagingBytes =
+      (MODE == GEMM_GROUPED_SILU_QUANT ? Cfg::kExchangeBytes : 0) + (kStaged ? kStoreWarps * kWarpStageBytes : 0);
+  static constexpr int kSmemLimit = 232448;  // 227 KB per CTA
+  static constexpr int kFit = (kSmemLimit - 1024 - 256 - kStagingBytes) / (Cfg::kStageA + Cfg::kStageB);
+  static constexpr int kStages = kFit > (BN == 256 ? 4 : 6) ? (BN == 256 ? 4 : 6) : kFit;
+  static constexpr size_t kSmemBytes = (size_t)kStages * (Cfg::kStageA + Cfg::kStageB) + kStagingBytes + 1024 + 256;
+  static_assert(kStages >= 3, "pipeline too shallow");
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
@@ -92,6 +111,34 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 // FP8 quantisation step that follows).
 __device__ __forceinline__ float silu_mul_fast(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+// eight floats -> eight 16-bit values in one 16-byte register quad
+template <typename OutT>
+__device__ __forceinline__ uint4 pack8(const float* a);
+template <>
+__device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float* a) {
+  uint4 v;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn(a[0], a[1]); v.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(a[2], a[3]); v.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(a[4], a[5]); v.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(a[6], a[7]); v.w = *reinterpret_cast<uint32_t*>(&t);
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 pack8<__half>(const float* a) {
+  uint4 v;
+  __half2 t;
+  t = __floats2half2_rn(a[0], a[1]); v.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(a[2], a[3]); v.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(a[4], a[5]); v.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(a[6], a[7]); v.w = *reinterpret_cast<uint32_t*>(&t);
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 pack8<float>(const float* a) {  // never staged; keeps the template total
+  return make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]), __float_as_uint(a[3]));
 }
 
 template <typename OutT>
@@ -144,18 +191,21 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 template <int BN, int MODE, typename OutT>
 __global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
 block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
-  constexpr int S = Cfg::kStages;
+  using L = GemmLayout<BN, MODE, OutT>;
+  constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const uint32_t sA = smem_base;
   const uint32_t sB = smem_base + S * Cfg::kStageA;
+  // after the stage ring (a multiple of 1024 bytes): [exchange (mode 1)] [output staging] [barriers]
   float* exchange = reinterpret_cast<float*>(smem_al + (size_t)S * (Cfg::kStageA + Cfg::kStageB));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + (size_t)S * (Cfg::kStageA + Cfg::kStageB) +
-                                               (MODE == GEMM_GROUPED_SILU_QUANT ? Cfg::kExchangeBytes : 0));
+  const uint32_t staging = smem_base + S * (Cfg::kStageA + Cfg::kStageB) +
+                           (MODE == GEMM_GROUPED_SILU_QUANT ? Cfg::kExchangeBytes : 0);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + (size_t)S * (Cfg::kStageA + Cfg::kStageB) + L::kStagingBytes);
   const uint32_t bar0 = ptx::smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
@@ -186,6 +236,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   if (warp == kProducerWarp && lane == 0) {
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    if (L::kStaged && MODE != GEMM_GROUPED_SCATTER) ptx::prefetch_tensormap(&tmap_c);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -371,6 +422,20 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // ------------------------------------------------------------ tile epilogue
       const int row = cur.row, col0 = cur.col0, nt = cur.nt, ks = cur.ks;
       const bool row_ok = cur.row_ok;
+      // this warp's staging area: kBoxesPerWarp boxes of [32 rows x 128 bytes], 128-byte swizzled
+      const int store_warp = MODE == GEMM_GROUPED_SILU_QUANT ? quarter : warp;
+      const uint32_t wstage = staging + store_warp * L::kWarpStageBytes;
+      // 16-byte chunk c of this thread's row (= lane) goes to box c/8, slot (c%8) ^ (lane%8)
+      auto stage_chunk = [&](int c, uint4 v) {
+        const uint32_t addr = wstage + (c >> 3) * 4096 + lane * 128 + (((c & 7) ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                     : "memory");
+      };
+      if (L::kStaged) {
+        // the bulk stores of the previous tile must have read the staging area before it is rewritten
+        if (MODE != GEMM_GROUPED_SCATTER && lane == 0) ptx::tma_store_wait_read();
+        __syncwarp();
+      }
       if (MODE == GEMM_GROUPED_SILU_QUANT) {
         if (p.topk_weights != nullptr) {
           // router weight applied to the gate_up product in fp32, before the activation (where
@@ -396,14 +461,13 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           named_bar_sync(1, Cfg::kEpiWarps * 32);
         }
-        if (half == 0 && row_ok) {
+        if (half == 0) {
           // this thread's 128 columns are exactly one 1x128 quantisation group
           float amax = 0.f;
 #pragma unroll
           for (int j = 0; j < 128; ++j) amax = fmaxf(amax, fabsf(acc[j]));
           amax = fmaxf(amax, 1e-10f);
           const float inv = __fdividef(448.0f, amax);
-          uint8_t* dst = p.q_out + (int64_t)row * p.N + col0;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             float q[16];
@@ -414,34 +478,88 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             v.y = pack4_e4m3(q[4], q[5], q[6], q[7]);
             v.z = pack4_e4m3(q[8], q[9], q[10], q[11]);
             v.w = pack4_e4m3(q[12], q[13], q[14], q[15]);
-            *reinterpret_cast<uint4*>(dst + 16 * j) = v;
+            stage_chunk(j, v);
           }
-          p.q_scales[(int64_t)nt * p.q_scale_ld + row] = __fdiv_rn(amax, 448.0f);
+          if (row_ok) p.q_scales[(int64_t)nt * p.q_scale_ld + row] = __fdiv_rn(amax, 448.0f);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {  // FP8 rows [32 x 128 B] of the expert-sorted activation
+            ptx::tma_store_3d(&tmap_c, wstage, col0, cur.mt * kBM + quarter * 32, 0);
+            ptx::tma_store_commit();
+          }
         }
       } else {
-        int64_t out_row = row;
-        bool store = row_ok;
+        float w = 1.f;
+        int flat = 0;
         if (MODE == GEMM_GROUPED_SCATTER) {
-          const int flat = store ? p.sorted_ids[row] : p.numel;
-          store = store && flat < p.numel;
-          out_row = flat;
-          if (store && p.topk_weights != nullptr) {
-            const float w = __ldg(p.topk_weights + flat);
-#pragma unroll
-            for (int j = 0; j < 128; ++j) acc[j] *= w;
-          }
+          flat = row_ok ? p.sorted_ids[row] : p.numel;  // (token, slot) this row belongs to; >= numel: pad
+          if (p.topk_weights != nullptr && flat < p.numel) w = __ldg(p.topk_weights + flat);
         }
-        if (store) {
-          OutT* dst = static_cast<OutT*>(p.C) + ks * p.split_stride + out_row * p.ldc + col0;
+        if (L::kStaged) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, acc + j * 8);
+          for (int c = 0; c < 16; ++c) {  // 16 chunks of 8 sixteen-bit elements
+            float t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = acc[c * 8 + i] * w;
+            stage_chunk(c, pack8<OutT>(t));
+          }
+          if (MODE == GEMM_DENSE) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              constexpr int kColsPerBox = 128 / (int)sizeof(OutT);
+#pragma unroll
+              for (int bxi = 0; bxi < L::kBoxesPerWarp; ++bxi) {
+                const int bx = bxi;
+                if (col0 + bx * kColsPerBox < p.N) {
+                  ptx::tma_store_3d(&tmap_c, wstage + bx * 4096, col0 + bx * kColsPerBox, cur.mt * kBM + quarter * 32, ks);
+                }
+              }
+              ptx::tma_store_commit();
+            }
+          } else {
+            // scatter: rows go to arbitrary (token, slot) positions; write each row as one
+            // contiguous run of 16-byte chunks, kRowBytes / 16 lanes per row
+            __syncwarp();
+            constexpr int kLanesPerRow = L::kRowBytes / 16;     // 16 (16-bit) or 32 (fp32)
+            constexpr int kRowsPerIter = 32 / kLanesPerRow;
+            const int c = lane % kLanesPerRow;
+#pragma unroll
+            for (int i = 0; i < 32 / kRowsPerIter; ++i) {
+              const int r = i * kRowsPerIter + lane / kLanesPerRow;
+              const int dst_flat = __shfl_sync(0xffffffffu, flat, r);
+              const uint32_t addr = wstage + (c >> 3) * 4096 + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+              uint4 v;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+              const int col = col0 + c * (16 / (int)sizeof(OutT));
+              if (dst_flat < p.numel && col < p.N)
+                *reinterpret_cast<uint4*>(static_cast<OutT*>(p.C) + (int64_t)dst_flat * p.ldc + col) = v;
+            }
+            __syncwarp();  // staging area free for the next tile
+          }
+        } else {
+          // fp32 output with 256-wide tiles: direct row stores
+          const bool store = row_ok && (MODE != GEMM_GROUPED_SCATTER || flat < p.numel);
+          if (store) {
+            const int64_t out_row = MODE == GEMM_GROUPED_SCATTER ? flat : row;
+            OutT* dst = static_cast<OutT*>(p.C) + ks * p.split_stride + out_row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float t[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) t[i] = acc[j * 8 + i] * w;
+              if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, t);
+            }
+          }
         }
       }
       cur = nxt;
       have = have_next;
     }
   }
+
+  // every bulk store of this CTA must have completed before its shared memory is released
+  if (L::kStaged && MODE != GEMM_GROUPED_SCATTER && warp < Cfg::kEpiWarps && lane == 0) ptx::tma_store_wait_all();
 
   // ---------------------------------------------------------------------- teardown
   if (*abort_flag) {

@@ -221,12 +221,18 @@ class FusedMoE:
     and GLOBAL expert ids."""
 
     def __init__(self, w1, w2, w1_s, w2_s, rank: int, size: int, mode: str = "ep", group=None,
-                 expert_fn: Optional[Callable] = None):
+                 expert_fn: Optional[Callable] = None, presharded: bool = False, num_experts: Optional[int] = None):
+        """``presharded``: the four tensors are already this rank's shard (a loader that never
+        materialises the full layer); ``num_experts`` then gives the global expert count."""
         assert mode in ("tp", "ep", "ep_a2a")
         self.mode, self.rank, self.size, self.group = mode, rank, size, group
-        self.num_experts = w1.shape[0]
-        shard = shard_moe_tp if mode == "tp" else shard_moe_ep
-        self.w1, self.w2, self.w1_s, self.w2_s = shard(w1, w2, w1_s, w2_s, rank, size)
+        if presharded:
+            self.num_experts = num_experts if num_experts is not None else w1.shape[0] * (1 if mode == "tp" else size)
+            self.w1, self.w2, self.w1_s, self.w2_s = w1, w2, w1_s, w2_s
+        else:
+            self.num_experts = w1.shape[0]
+            shard = shard_moe_tp if mode == "tp" else shard_moe_ep
+            self.w1, self.w2, self.w1_s, self.w2_s = shard(w1, w2, w1_s, w2_s, rank, size)
         self.dispatcher = AllToAllDispatcher(self.num_experts, rank, size, group) if mode == "ep_a2a" else None
         self._expert_fn = expert_fn  # tests on CPU inject a stand-in for the CUDA kernels
 

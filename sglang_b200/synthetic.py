@@ -45,16 +45,18 @@ def weight(N: int, K: int, seed: int, device="cpu"):
     return block_quant_weight_fp8(w)
 
 
-def expert_weights(E: int, I: int, H: int, seed: int, device="cuda"):
-    """Per-expert N(0, 0.02^2) weights. Generated on ``device`` from a per-expert seed (the
-    DeepSeek-V3 layer is 11.3 GB of FP8: too slow to draw on the host), then block-quantised."""
+def expert_weights(E: int, I: int, H: int, seed: int, device="cuda", first_expert: int = 0):
+    """Per-expert N(0, 0.02^2) weights for experts ``[first_expert, first_expert + E)``.
+    Generated on ``device`` from a per-expert seed (the DeepSeek-V3 layer is 11.3 GB of FP8: too
+    slow to draw on the host; an expert-parallel rank draws only its own experts), then
+    block-quantised."""
     w1 = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn, device=device)
     w2 = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=device)
     w1_s = torch.empty(E, 2 * I // 128, H // 128, dtype=torch.float32, device=device)
     w2_s = torch.empty(E, H // 128, I // 128, dtype=torch.float32, device=device)
     g = torch.Generator(device=device)
     for e in range(E):
-        g.manual_seed(seed * 100003 + e)
+        g.manual_seed(seed * 100003 + first_expert + e)
         a = (torch.randn(2 * I, H, generator=g, device=device) * 0.02).bfloat16()
         w1[e], w1_s[e] = block_quant_weight_fp8(a)
         b = (torch.randn(H, I, generator=g, device=device) * 0.02).bfloat16()
