@@ -17,36 +17,49 @@ namespace b200 {
 
 constexpr int kMoeBlockM = 128;
 
-// One thread = 16 consecutive elements of one sorted row (8 lanes share a 128-group).
+// One thread = 16 consecutive elements of kGatherRows consecutive sorted rows (8 lanes share a
+// 128-group). blockIdx.x = group of rows, blockIdx.y = 256-chunk segment of the row. The row
+// indices and then the row data of all kGatherRows rows are requested before any is used, so
+// the dependent index -> data round trips overlap instead of adding up per row.
+constexpr int kGatherRows = 4;  // divides the 128-row expert blocks
+
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
     const T* __restrict__ hidden, const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
-    const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q,
-    float* __restrict__ s, int64_t total_chunks, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t slot = c / chunks_per_row;
-  const int chunk = (int)(c - slot * chunks_per_row);
-  bool active = c < total_chunks && slot < *num_post_pad;
-  if (active) active = expert_ids[slot / kMoeBlockM] >= 0;
-  int flat = numel;
-  if (active) flat = sorted_ids[slot];
-  const bool real = active && flat < numel;
-  float f[16];
-  if (real) {
-    Vec16<T>::load(hidden + (int64_t)(flat / topk) * H + chunk * 16, f);
-  } else {
+    const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q, float* __restrict__ s, int chunks_per_row,
+    int64_t H, int numel, int topk, int64_t cap) {
+  const int64_t slot0 = (int64_t)blockIdx.x * kGatherRows;
+  if (slot0 >= *num_post_pad || expert_ids[slot0 / kMoeBlockM] < 0) return;  // uniform per block
+  const int chunk = blockIdx.y * blockDim.x + threadIdx.x;
+  const bool active = chunk < chunks_per_row;  // whole 8-lane groups are in or out (H % 128 == 0)
+  int flat[kGatherRows];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) f[i] = 0.f;
+  for (int r = 0; r < kGatherRows; ++r) flat[r] = __ldg(sorted_ids + slot0 + r);
+  constexpr int kRegs = 16 * (int)sizeof(T) / 16;  // 16-byte registers per 16 elements
+  uint4 raw[kGatherRows][kRegs];
+#pragma unroll
+  for (int r = 0; r < kGatherRows; ++r) {
+    const bool real = active && flat[r] < numel;
+    const T* src = hidden + (int64_t)(real ? flat[r] / topk : 0) * H + chunk * 16;
+#pragma unroll
+    for (int i = 0; i < kRegs; ++i) raw[r][i] = real ? ld_nc_16(src + i * (16 / (int)sizeof(T))) : make_uint4(0, 0, 0, 0);
   }
-  float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-  amax = fmaxf(group_max<8>(amax), 1e-10f);
-  uint4 out;
-  const float scale = quant16(f, amax, B200_QUANT_DIV, out);
-  if (active) {  // pad rows of live blocks are written as zeros so the GEMM reads defined bytes
-    *reinterpret_cast<uint4*>(q + slot * H + chunk * 16) = out;
-    if ((threadIdx.x & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot] = scale;
+  for (int r = 0; r < kGatherRows; ++r) {
+    float f[16];
+    const T* e = reinterpret_cast<const T*>(raw[r]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = to_f32<T>(e[i]);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    amax = fmaxf(group_max<8>(amax), 1e-10f);
+    uint4 out;
+    const float scale = quant16(f, amax, B200_QUANT_DIV, out);
+    if (active) {  // pad rows of live blocks are written as zeros so the GEMM reads defined bytes
+      *reinterpret_cast<uint4*>(q + (slot0 + r) * H + chunk * 16) = out;
+      if ((threadIdx.x & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot0 + r] = scale;
+    }
   }
 }
 
@@ -55,12 +68,11 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
 __global__ void __launch_bounds__(256) moe_gather_fp8_kernel(
     const uint8_t* __restrict__ hidden_q, const float* __restrict__ hidden_s, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q,
-    float* __restrict__ s, int64_t total_chunks, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t slot = c / chunks_per_row;
-  const int chunk = (int)(c - slot * chunks_per_row);
-  if (c >= total_chunks || slot >= *num_post_pad) return;
-  if (expert_ids[slot / kMoeBlockM] < 0) return;
+    float* __restrict__ s, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
+  const int64_t slot = blockIdx.x;
+  if (slot >= *num_post_pad || expert_ids[slot / kMoeBlockM] < 0) return;
+  const int chunk = blockIdx.y * blockDim.x + threadIdx.x;
+  if (chunk >= chunks_per_row) return;
   const int flat = sorted_ids[slot];
   uint4 v = make_uint4(0, 0, 0, 0);
   float sc = 0.f;
@@ -160,14 +172,15 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   }
   {
     const int cpr = (int)(H / 16);
-    const int64_t total = L.cap * cpr;
+    const int threads = cpr < 256 ? (cpr + 31) / 32 * 32 : 256;  // whole warps; cpr is a multiple of 8
+    dim3 grid((unsigned)L.cap, (unsigned)cdiv(cpr, threads));
+    if (hidden_scale == nullptr) grid.x = (unsigned)(L.cap / kGatherRows);
     if (hidden_scale != nullptr)
-      moe_gather_fp8_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
-          static_cast<const uint8_t*>(hidden), hidden_scale, sorted, expert_ids, npp, aq1, as1, total, cpr, H,
-          (int)numel, topk, L.cap);
+      moe_gather_fp8_kernel<<<grid, threads, 0, st>>>(static_cast<const uint8_t*>(hidden), hidden_scale, sorted,
+                                                     expert_ids, npp, aq1, as1, cpr, H, (int)numel, topk, L.cap);
     else
-      moe_gather_quant_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
-          static_cast<const T*>(hidden), sorted, expert_ids, npp, aq1, as1, total, cpr, H, (int)numel, topk, L.cap);
+      moe_gather_quant_kernel<T><<<grid, threads, 0, st>>>(static_cast<const T*>(hidden), sorted, expert_ids, npp, aq1,
+                                                          as1, cpr, H, (int)numel, topk, L.cap);
     if ((rc = check_launch("moe_gather"))) return rc;
   }
   int force_bn = 0;
