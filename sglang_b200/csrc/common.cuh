@@ -145,8 +145,7 @@ __device__ __forceinline__ float quant16(const float (&f)[16], float amax, int f
 #pragma unroll
     for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(f[i], s);
   }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) q[i] = fminf(fmaxf(q[i], -448.0f), 448.0f);
+  // no explicit clamp to +-448: the conversion below saturates finite values to the same result
   out.x = pack4_e4m3(q[0], q[1], q[2], q[3]);
   out.y = pack4_e4m3(q[4], q[5], q[6], q[7]);
   out.z = pack4_e4m3(q[8], q[9], q[10], q[11]);

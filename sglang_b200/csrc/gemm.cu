@@ -3,6 +3,7 @@
 #include <stdlib.h>
 
 #include "gemm_host.cuh"
+#include "gemm_skinny.cuh"
 
 namespace b200 {
 
@@ -30,9 +31,15 @@ static int launch_reduce(const float* partial, void* C, int64_t mn, int splits, 
 
 }  // namespace b200
 
+namespace b200 {
+constexpr int64_t kSkinnyMaxM = 64;  // rows up to which the swapped-operand decode kernel is used
+}
+
 extern "C" size_t b200_w8a8_block_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const int s = b200::choose_k_splits(M, N, K, 148);  // sized for the largest split any SM count <= 148 picks
+  // sized for the largest split any SM count <= 148 picks
+  const int s = M <= b200::kSkinnyMaxM ? b200::skinny_k_splits(M, N, K, b200::skinny_token_tile(M), 148)
+                                       : b200::choose_k_splits(M, N, K, 148);
   return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
 
@@ -59,9 +66,36 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_CHECK_ARG(c_dtype == B200_BF16 || c_dtype == B200_F16 || c_dtype == B200_F32, "gemm: unknown output dtype code %d",
                  c_dtype);
-  int splits = choose_k_splits(M, N, K, sm_count() < 148 ? sm_count() : 148);
+  const int sms = sm_count() < 148 ? sm_count() : 148;
+  const char* skinny_env = getenv("B200_GEMM_SKINNY");  // test hook: 0 disables the decode kernel
+  const bool skinny = M <= kSkinnyMaxM && force_bn == 0 && !(skinny_env && atoi(skinny_env) == 0);
+  int splits = skinny ? skinny_k_splits(M, N, K, skinny_token_tile(M), sms) : choose_k_splits(M, N, K, sms);
   if (const char* e = getenv("B200_GEMM_SPLITK")) splits = atoi(e) > 0 ? atoi(e) : splits;  // test hook
   if (splits > (int)cdiv(K, 128)) splits = (int)cdiv(K, 128);
+  if (skinny) {
+    while (cdiv(cdiv(K, 128), splits) > SkinnyCfg<16>::kMaxKb) ++splits;  // scales of one item fit its smem table
+    SkinnyParams sp = {};
+    sp.As = As; sp.as_sm = as_stride_m; sp.as_sk = as_stride_k; sp.Bs = Bs;
+    sp.M = (int)M; sp.N = (int)N; sp.K = (int)K;
+    if (splits == 1) {
+      sp.C = C;
+      if (c_dtype == B200_BF16) return launch_skinny<__nv_bfloat16>(A, B, sp, 1, st);
+      if (c_dtype == B200_F16) return launch_skinny<__half>(A, B, sp, 1, st);
+      return launch_skinny<float>(A, B, sp, 1, st);
+    }
+    const size_t need = (size_t)splits * (size_t)M * (size_t)N * sizeof(float);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) != 0) {
+      set_error_detail("gemm: split-K needs a 16-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
+      return B200_E_WORKSPACE;
+    }
+    sp.C = workspace;
+    int rc = launch_skinny<float>(A, B, sp, splits, st);
+    if (rc) return rc;
+    const float* part = static_cast<const float*>(workspace);
+    if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st);
+    if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st);
+    return launch_reduce<float>(part, C, M * N, splits, st);
+  }
   if (splits > 1) {
     // decode-sized problem: fp32 partials per K split in the workspace, then one reduction pass
     const size_t need = (size_t)splits * (size_t)M * (size_t)N * sizeof(float);

@@ -26,7 +26,8 @@ def test_workspace_queries_need_no_gpu():
     lib = _native.load()
     assert lib.b200_moe_align_workspace_bytes(1024, 257) == 0
     assert lib.b200_moe_align_workspace_bytes(131072, 257) == 128 * 257 * 4
-    assert lib.b200_w8a8_block_fp8_gemm_workspace_bytes(64, 2048, 2048) == 4 * 64 * 2048 * 4  # split-K partials
+    ws = lib.b200_w8a8_block_fp8_gemm_workspace_bytes(64, 2048, 2048)  # split-K fp32 partials
+    assert ws > 0 and ws % (64 * 2048 * 4) == 0 and ws // (64 * 2048 * 4) <= 16
     assert lib.b200_w8a8_block_fp8_gemm_workspace_bytes(8192, 4096, 4096) == 0
     assert lib.b200_fused_experts_fp8_workspace_bytes(16, 2, 8, 256, 128) > 0
 

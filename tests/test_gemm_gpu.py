@@ -88,6 +88,33 @@ def test_split_k(M, N, K, splitk):
     _case(M, N, K, 301 + M + splitk, splitk=splitk, out_dtype=torch.float32)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize(
+    "M,N,K", [(1, 128, 128), (3, 320, 384), (16, 1088, 512), (17, 256, 1024), (33, 640, 320), (64, 512, 2048),
+              (40, 4096, 4096), (8, 256, 8320)]
+)
+def test_decode_kernel(M, N, K, dtype):
+    # M <= 64 runs the swapped-operand kernel: 16- and 32-token tiles, two token tiles, ragged N and K,
+    # its own split-K choice, and more K blocks than one work item may hold (K = 8320 -> 65 blocks)
+    _case(M, N, K, 400 + M + N, out_dtype=dtype)
+
+
+def test_decode_kernel_matches_large_tile_kernel():
+    import sglang_b200 as S
+
+    A, B = _rand_fp8((48, 1024), 1).cuda(), _rand_fp8((768, 1024), 2).cuda()
+    g = torch.Generator().manual_seed(3)
+    As, Bs = (torch.rand(48, 8, generator=g) * 1e-2).cuda(), (torch.rand(6, 8, generator=g) * 1e-2).cuda()
+    c1 = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.float32)
+    os.environ["B200_GEMM_SKINNY"] = "0"
+    try:
+        c2 = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.float32)
+    finally:
+        os.environ.pop("B200_GEMM_SKINNY", None)
+    _status_ok()
+    assert float((c1 - c2).norm() / c2.norm()) < 1e-5
+
+
 def test_many_tiles_persistent_loop():
     # more tiles than SMs so every CTA walks several tiles and the barrier phases wrap
     _case(1024, 6144, 1024, 9)
