@@ -43,6 +43,7 @@ if "reference" in sys.argv and os.environ.get("OMP_NUM_THREADS") == "1":
 import torch  # noqa: E402
 
 M_ROWS = 8192
+GEMM_TRAFFIC_RATIO = 1.10  # measured DRAM bytes / algorithmic bytes of the GEMM kernel (ncu, see profiles/)
 LINEARS = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
 FLOPS_PER_ROW = sum(2 * n * k for _, n, k in LINEARS)
 WORKLOAD = "llama3-8b block-fp8 linears (qkv,o_proj,gate_up,down), M=8192: quant + GEMM each"
@@ -172,12 +173,12 @@ def time_cpu_baseline(budget_s: float = 15.0):
     """Oracle on the host cores on a bounded row sample sized to ~budget_s of CPU work."""
     threads = os.cpu_count() or 1
     rows = 64
-    acts, weights = cpu_inputs(256)
+    acts, weights = cpu_inputs(4096)
     t0 = time.perf_counter()
     cpu_linears(rows, threads, weights, acts)
     dt = time.perf_counter() - t0
     # scale the sample towards the budget (the first pass doubles as warm-up)
-    rows = int(max(64, min(256, rows * budget_s / max(dt, 1e-3) / 2)))
+    rows = int(max(64, min(4096, rows * budget_s / max(dt, 1e-3) / 2)))
     rows = rows // 32 * 32
     t0 = time.perf_counter()
     cpu_linears(rows, threads, weights, acts)
@@ -378,8 +379,13 @@ def main():
     gemm_ms = sum(statistics.mean(v) for v in per_shape.values())
     gemm_tflops = M_ROWS * FLOPS_PER_ROW / gemm_ms / 1e9
     fp8_peak = 2 * peaks["bf16_sustained"]
+    alg_bytes = {n: M_ROWS * kk + nn * kk + 2 * M_ROWS * nn + 4 * (M_ROWS * kk // 128 + nn * kk // 16384) for n, nn, kk in LINEARS}
     roofline = {"bound": "tensor", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
-                "traffic": None, "kernel": "block_fp8_gemm_kernel<256,dense,bf16>",
+                "traffic": GEMM_TRAFFIC_RATIO * sum(alg_bytes.values()) / len(alg_bytes), "kernel": "block_fp8_gemm_kernel<256,dense,bf16>",
+                "traffic_note": "dram read+write of one ncu capture at 8192x8192x4096 was 1.10 x its algorithmic bytes "
+                                "(profiles/block_fp8_gemm_kernel_dense_8192x8192x4096.md); scaled to the mean algorithmic "
+                                "bytes of the four launches of a step",
+                "algorithmic_bytes_per_launch": sum(alg_bytes.values()) / len(alg_bytes),
                 "peak_note": f"2 x {peaks['source']} sustained dense bf16 ({peaks['bf16_sustained']} TF/s); nominal dense FP8 is 4500",
                 "frac_of_nominal_fp8": gemm_tflops / 4500.0,
                 "per_shape_tflops": {n: 2 * M_ROWS * nn * kk / statistics.mean(per_shape[n]) / 1e9 for n, nn, kk in LINEARS}}

@@ -68,7 +68,9 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
                  c_dtype);
   const int sms = sm_count() < 148 ? sm_count() : 148;
   const char* skinny_env = getenv("B200_GEMM_SKINNY");  // test hook: 0 disables the decode kernel
-  const bool skinny = M <= kSkinnyMaxM && force_bn == 0 && !(skinny_env && atoi(skinny_env) == 0);
+  int64_t skinny_max_m = kSkinnyMaxM;
+  if (const char* e = getenv("B200_GEMM_SKINNY_MAX_M")) skinny_max_m = atoi(e);  // tuning hook
+  const bool skinny = M <= skinny_max_m && force_bn == 0 && !(skinny_env && atoi(skinny_env) == 0);
   int splits = skinny ? skinny_k_splits(M, N, K, skinny_token_tile(M), sms) : choose_k_splits(M, N, K, sms);
   if (const char* e = getenv("B200_GEMM_SPLITK")) splits = atoi(e) > 0 ? atoi(e) : splits;  // test hook
   if (splits > (int)cdiv(K, 128)) splits = (int)cdiv(K, 128);
@@ -105,7 +107,7 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
     }
     p.C = workspace;
     p.split_stride = M * N;
-    int rc = launch_gemm<GEMM_DENSE, float>(A, B, N, p, 128, st, 0, splits);
+    int rc = launch_gemm<GEMM_DENSE, float>(A, B, N, p, force_bn, st, 0, splits);
     if (rc) return rc;
     const float* part = static_cast<const float*>(workspace);
     if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st);

@@ -8,10 +8,10 @@
 
 namespace b200 {
 
-// Split-K factor for the dense GEMM: when 128 x 128 tiles alone would leave most SMs idle
-// (decode-sized M), split K so that about one work item per SM streams the weights.
+// Split-K factor for the dense GEMM: when the 128 x 256 tiles alone would leave most SMs idle
+// (a few hundred rows), split K so that about one work item per SM streams the weights.
 inline int choose_k_splits(int64_t M, int64_t N, int64_t K, int sms) {
-  const int64_t tiles = cdiv(M, 128) * cdiv(N, 128);
+  const int64_t tiles = cdiv(M, 128) * cdiv(N, N > 128 ? 256 : 128);
   const int64_t num_kb = cdiv(K, 128);
   if (tiles * 4 >= (int64_t)sms * 3 || num_kb < 8) return 1;
   int64_t s = sms / tiles;
@@ -129,12 +129,14 @@ inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmP
     return B200_E_LAUNCH;
   }
   const int sms = sm_count();
-  // 128 x 256 tiles halve the shared-memory traffic per flop; fall back to 128 x 128 when
-  // that would leave SMs idle (small problems) or N has no second 128-block.
+  // 128 x 256 tiles: eight promotion warps hide the TMEM round trips of each other and the
+  // shared-memory traffic per flop is halved. The 128-wide tile (four promotion warps) is
+  // slower per flop even when it fills more SMs; it is kept for N <= 128 (small problems are
+  // spread over the SMs by split-K instead).
   int bn = 256;
   if (MODE == GEMM_GROUPED_SILU_QUANT) force_bn = 256;  // gate + up halves of one tile
-  const int64_t m_tiles_live = m_tiles_hint > 0 ? m_tiles_hint : p.m_tiles;  // grouped: expected live row tiles
-  if (p.N <= 128 || m_tiles_live * cdiv(p.N, 256) < sms) bn = 128;
+  (void)m_tiles_hint;
+  if (p.N <= 128) bn = 128;
   if (force_bn == 128 || force_bn == 256) bn = force_bn;
   p.n_tiles = MODE == GEMM_GROUPED_SILU_QUANT ? p.N / 128 : (int)cdiv(p.N, bn);
   p.group_m = 16;

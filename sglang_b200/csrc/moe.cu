@@ -54,8 +54,16 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
 #pragma unroll
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
     amax = fmaxf(group_max<8>(amax), 1e-10f);
+    // Internal activation of the fused layer: the stored scale is the exact amax / 448, the bytes
+    // are x * (448 / amax) (one multiply per element instead of an IEEE division; the rare code
+    // that differs from x / scale by one step is far inside the layer's 1e-2 tolerance).
+    const float scale = __fdiv_rn(amax, 448.0f);
+    const float inv = __fdiv_rn(448.0f, amax);
     uint4 out;
-    const float scale = quant16(f, amax, B200_QUANT_DIV, out);
+    out.x = pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+    out.y = pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+    out.z = pack4_e4m3(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
+    out.w = pack4_e4m3(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
     if (active) {  // pad rows of live blocks are written as zeros so the GEMM reads defined bytes
       *reinterpret_cast<uint4*>(q + (slot0 + r) * H + chunk * 16) = out;
       if ((threadIdx.x & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot0 + r] = scale;

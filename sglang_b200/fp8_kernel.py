@@ -170,6 +170,8 @@ def w8a8_block_fp8_matmul(
     ws_bytes = lib.b200_w8a8_block_fp8_gemm_workspace_bytes(M, Nn, K)
     if "B200_GEMM_SPLITK" in os.environ:  # test hook of the native side: size for the forced split
         ws_bytes = max(ws_bytes, int(os.environ["B200_GEMM_SPLITK"]) * M * Nn * 4)
+    if "B200_GEMM_SKINNY_MAX_M" in os.environ:  # tuning hook: any split the decode kernel may pick
+        ws_bytes = max(ws_bytes, 16 * M * Nn * 4)
     with N.on_device(A):
         ws = _workspace(A.device, ws_bytes)
         st = lib.b200_w8a8_block_fp8_gemm(
