@@ -348,6 +348,7 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout to the one JSON line
         torch.distributed.init_process_group("nccl", device_id=device)
     import sglang_b200 as S
     from sglang_b200 import _native

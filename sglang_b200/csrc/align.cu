@@ -142,28 +142,48 @@ __global__ void __launch_bounds__(kAlignThreads) align_hist_kernel(const IdT* __
 }
 
 // One block: turns chunk_hist[c][b] into the global position of chunk c's first id of bucket b.
+// Threads are laid out as (segment, bucket): kAlignThreads / B' segments (B' = buckets rounded up
+// to a power of two <= 1024) each own a contiguous range of chunks, so the strided loads of one
+// bucket are spread over several threads instead of being one long dependent chain.
 __global__ void __launch_bounds__(kAlignThreads) align_scan_kernel(int32_t* __restrict__ chunk_hist, int chunks, int B,
                                                                    int block_size, int32_t* __restrict__ expert_ids,
                                                                    int64_t max_blocks, int32_t* __restrict__ num_post_pad,
                                                                    int32_t* __restrict__ cumsum) {
   extern __shared__ int smem[];
-  int* cnt = smem;       // [B]
-  int* start = cnt + B;  // [B+1]
+  int* cnt = smem;            // [B]
+  int* start = cnt + B;       // [B+1]
+  int* seg_sum = start + B + 1;  // [segs][B]: ids of bucket b in the chunks of segment s
   __shared__ int warp_sums[32];
   const int tid = threadIdx.x;
-  for (int b = tid; b < B; b += kAlignThreads) {
+  int bp = 32;
+  while (bp < B && bp < kAlignThreads) bp <<= 1;
+  const int segs = B > kAlignThreads ? 1 : kAlignThreads / bp;
+  const int per_seg = (chunks + segs - 1) / segs;
+  for (int b = tid % bp, sgm = tid / bp; b < B && sgm < segs; b += bp) {  // b += bp only loops when B > 1024
+    const int c0 = sgm * per_seg, c1 = min(chunks, c0 + per_seg);
     int run = 0;
 #pragma unroll 8
-    for (int c = 0; c < chunks; ++c) run += chunk_hist[(int64_t)c * B + b];
+    for (int c = c0; c < c1; ++c) run += chunk_hist[(int64_t)c * B + b];
+    seg_sum[sgm * B + b] = run;
+  }
+  __syncthreads();
+  for (int b = tid; b < B; b += kAlignThreads) {
+    int run = 0;
+    for (int sgm = 0; sgm < segs; ++sgm) {
+      const int t = seg_sum[sgm * B + b];
+      seg_sum[sgm * B + b] = run;  // ids of bucket b in earlier segments
+      run += t;
+    }
     cnt[b] = run;
   }
   __syncthreads();
   bucket_scan(cnt, start, B, block_size, warp_sums);
   write_block_outputs(cnt, start, B, block_size, expert_ids, max_blocks, num_post_pad, cumsum);
-  for (int b = tid; b < B; b += kAlignThreads) {
-    int run = start[b];
+  for (int b = tid % bp, sgm = tid / bp; b < B && sgm < segs; b += bp) {
+    const int c0 = sgm * per_seg, c1 = min(chunks, c0 + per_seg);
+    int run = start[b] + seg_sum[sgm * B + b];
 #pragma unroll 8
-    for (int c = 0; c < chunks; ++c) {
+    for (int c = c0; c < c1; ++c) {
       const int t = chunk_hist[(int64_t)c * B + b];
       chunk_hist[(int64_t)c * B + b] = run;
       run += t;
@@ -204,7 +224,10 @@ static int launch_align(const void* ids_, int64_t numel, int B, int block_size, 
   const int chunks = (int)cdiv(numel, kAlignThreads);
   int32_t* chunk_hist = static_cast<int32_t*>(ws);
   align_hist_kernel<IdT><<<chunks, kAlignThreads, (size_t)B * sizeof(int), st>>>(ids, numel, B, sorted, max_pad, chunk_hist);
-  align_scan_kernel<<<1, kAlignThreads, (size_t)(2 * B + 1) * sizeof(int), st>>>(chunk_hist, chunks, B, block_size,
+  int bp = 32;
+  while (bp < B && bp < kAlignThreads) bp <<= 1;
+  const int segs = B > kAlignThreads ? 1 : kAlignThreads / bp;
+  align_scan_kernel<<<1, kAlignThreads, (size_t)(2 * B + 1 + segs * B) * sizeof(int), st>>>(chunk_hist, chunks, B, block_size,
                                                                                expert_ids, max_blocks, num_post_pad, cumsum);
   auto k = align_scatter_kernel<IdT>;
   if (rank_smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rank_smem);
