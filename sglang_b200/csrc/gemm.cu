@@ -3,6 +3,7 @@
 #include <stdlib.h>
 
 #include "gemm_host.cuh"
+#include "gemm_2cta.cuh"
 #include "gemm_skinny.cuh"
 
 namespace b200 {
@@ -33,6 +34,7 @@ static int launch_reduce(const float* partial, void* C, int64_t mn, int splits, 
 
 namespace b200 {
 constexpr int64_t kSkinnyMaxM = 64;  // rows up to which the swapped-operand decode kernel is used
+constexpr bool kPairedByDefault = false;  // CTA-pair kernel for large dense problems
 }
 
 extern "C" size_t b200_w8a8_block_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
@@ -113,6 +115,17 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
     if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st);
     if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st);
     return launch_reduce<float>(part, C, M * N, splits, st);
+  }
+  // Large dense problems with 16-bit output: CTA pairs (each CTA loads half of the B tile)
+  {
+    const char* e2 = getenv("B200_GEMM_2CTA");  // hook: 0 = never, 1 = whenever legal
+    const int mode2 = e2 ? atoi(e2) : -1;
+    const bool legal = c_dtype != B200_F32 && force_bn == 0 && N >= 256;
+    const bool want = mode2 == 1 || (mode2 != 0 && kPairedByDefault && M >= 1024 && cdiv(M, 256) * cdiv(N, 256) >= 64);
+    if (legal && want) {
+      if (c_dtype == B200_BF16) return launch_gemm_2cta<__nv_bfloat16>(A, B, p, st);
+      return launch_gemm_2cta<__half>(A, B, p, st);
+    }
   }
   switch (c_dtype) {
     case B200_BF16: return launch_gemm<GEMM_DENSE, __nv_bfloat16>(A, B, N, p, force_bn, st);

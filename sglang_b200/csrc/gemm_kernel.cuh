@@ -311,8 +311,10 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
           for (int k = 0; k < kBK / 32; ++k)  // +32 bytes along K inside the swizzle row = +2 in the address field
             ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, k > 0);  // k == 0 overwrites the buffer
-          ptx::mma_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
-          ptx::mma_commit(tfull_bar(b));   // partial product ready for the promotion warps
+          // One commit per K block: partial product ready for the promotion warps. (The smem
+          // stage is released by promotion warp 0 once it sees this barrier: a second commit
+          // here costs the issuing thread more than a hundred cycles per K block.)
+          ptx::mma_commit(tfull_bar(b));
         }
         __syncwarp();
       }
@@ -377,42 +379,48 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
 
-      for (int kb = cur.kb0; kb < cur.kb1; ++kb, ++it) {
-        const int b = it & 1;
-        // scales are multiplied only when used, four K blocks after their loads were issued
-        const float sc = cur.a_pf[0] * cur.b_pf[0];
+      // The scale registers form a ring of four: K block kb uses slot (kb - kb0) % 4 and refills it
+      // for kb + 4. The loop is unrolled by four so the slots are fixed registers (a rotating
+      // copy would read the value loaded one iteration ago and wait a full L2 round trip).
+      for (int kbase = cur.kb0; kbase < cur.kb1 && ok; kbase += 4) {
 #pragma unroll
-        for (int d = 0; d < 3; ++d) {
-          cur.a_pf[d] = cur.a_pf[d + 1];
-          cur.b_pf[d] = cur.b_pf[d + 1];
+        for (int j = 0; j < 4; ++j) {
+          const int kb = kbase + j;
+          if (kb >= cur.kb1 || !ok) break;
+          const int b = it & 1;
+          const float sc = cur.a_pf[j] * cur.b_pf[j];
+          {
+            const bool in = cur.row_ok && kb + 4 < cur.kb1;
+            cur.a_pf[j] = in ? __ldg(cur.as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
+            cur.b_pf[j] = in ? __ldg(cur.bs_ptr + kb + 4) : 0.f;
+          }
+          ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
+          if (!ok) break;
+          // the MMAs of this K block have completed, so they have also finished reading their
+          // shared-memory stage: hand it back to the TMA producer
+          if (warp == 0 && lane == 0) ptx::mbar_arrive(empty_bar(it % S));
+          ptx::tc_fence_after();
+          const uint32_t ta = lane_base + b * BN;
+          uint32_t va[32], vb[32];
+          // one TMEM load in flight behind the FMAs of the previous 32 columns
+          ptx::tmem_ld32(ta, va);
+          ptx::tmem_ld_wait(va);
+          ptx::tmem_ld32(ta + 32, vb);
+          promote32(acc, va, sc);
+          ptx::tmem_ld_wait(vb);
+          ptx::tmem_ld32(ta + 64, va);
+          promote32(acc + 32, vb, sc);
+          ptx::tmem_ld_wait(va);
+          ptx::tmem_ld32(ta + 96, vb);
+          promote32(acc + 64, va, sc);
+          ptx::tmem_ld_wait(vb);
+          // every TMEM read of this buffer has landed: give it back to the MMA warp
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
+          promote32(acc + 96, vb, sc);
+          ++it;
         }
-        {
-          const bool in = cur.row_ok && kb + 4 < cur.kb1;
-          cur.a_pf[3] = in ? __ldg(cur.as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
-          cur.b_pf[3] = in ? __ldg(cur.bs_ptr + kb + 4) : 0.f;
-        }
-        ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
-        if (!ok) break;
-        ptx::tc_fence_after();
-        const uint32_t ta = lane_base + b * BN;
-        uint32_t va[32], vb[32];
-        // one TMEM load in flight behind the FMAs of the previous 32 columns
-        ptx::tmem_ld32(ta, va);
-        ptx::tmem_ld_wait(va);
-        ptx::tmem_ld32(ta + 32, vb);
-        promote32(acc, va, sc);
-        ptx::tmem_ld_wait(vb);
-        ptx::tmem_ld32(ta + 64, va);
-        promote32(acc + 32, vb, sc);
-        ptx::tmem_ld_wait(va);
-        ptx::tmem_ld32(ta + 96, vb);
-        promote32(acc + 64, va, sc);
-        ptx::tmem_ld_wait(vb);
-        // every TMEM read of this buffer has landed: give it back to the MMA warp
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-        promote32(acc + 96, vb, sc);
       }
       if (!ok) break;
 
