@@ -332,6 +332,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     // of its scales (and of its expert id) overlap the stores instead of stalling the MMA.
     struct Item {
       int item, mt, nt, ks, kb0, kb1, expert, row, col0;
+      int flat;  // scatter mode: (token, slot) index of this thread's row, >= numel for a pad row
       bool row_ok;
       const float* as_ptr;
       const float* bs_ptr;
@@ -359,6 +360,8 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int nb = MODE == GEMM_GROUPED_SILU_QUANT ? half * p.n_blocks + c.nt : min(c.col0 / 128, p.n_blocks - 1);
         const int bs_rows = MODE == GEMM_GROUPED_SILU_QUANT ? 2 * p.n_blocks : p.n_blocks;
         c.bs_ptr = p.Bs + ((int64_t)c.expert * bs_rows + nb) * num_kb;
+        c.flat = 0;
+        if (MODE == GEMM_GROUPED_SCATTER) c.flat = c.row_ok ? __ldg(p.sorted_ids + c.row) : p.numel;
 #pragma unroll
         for (int d = 0; d < 4; ++d) {
           const bool in = c.row_ok && c.kb0 + d < c.kb1;
@@ -378,6 +381,11 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      // scatter mode: the router weight of this row, requested now (its index was fetched one tile
+      // ahead) and used only in the epilogue
+      float row_weight = 1.f;
+      if (MODE == GEMM_GROUPED_SCATTER && p.topk_weights != nullptr && cur.flat < p.numel)
+        row_weight = __ldg(p.topk_weights + cur.flat);
 
       // The scale registers form a ring of four: K block kb uses slot (kb - kb0) % 4 and refills it
       // for kb + 4. The loop is unrolled by four so the slots are fixed registers (a rotating
@@ -497,12 +505,8 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
       } else {
-        float w = 1.f;
-        int flat = 0;
-        if (MODE == GEMM_GROUPED_SCATTER) {
-          flat = row_ok ? p.sorted_ids[row] : p.numel;  // (token, slot) this row belongs to; >= numel: pad
-          if (p.topk_weights != nullptr && flat < p.numel) w = __ldg(p.topk_weights + flat);
-        }
+        const float w = row_weight;
+        const int flat = cur.flat;  // (token, slot) this row belongs to; >= numel: pad
         if (L::kStaged) {
 #pragma unroll
           for (int c = 0; c < 16; ++c) {  // 16 chunks of 8 sixteen-bit elements
