@@ -149,7 +149,7 @@ inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmP
   int rc = make_tmap_u8(&ta, A, (uint64_t)p.M, (uint64_t)p.K, kBM, "A");
   if (rc) return rc;
   rc = make_tmap_u8(&tb, B, (uint64_t)b_rows_total, (uint64_t)p.K,
-                    MODE == GEMM_GROUPED_SILU_QUANT ? 128u : (uint32_t)bn, "B");
+                    MODE == GEMM_GROUPED_SILU_QUANT ? 64u : (uint32_t)bn, "B");
   if (rc) return rc;
   // output map: dense -> C [splits, M, N]; gate_up -> FP8 activation [cap, I]; scatter -> unused
   CUtensorMap tc = ta;

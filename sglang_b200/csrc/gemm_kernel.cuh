@@ -16,9 +16,11 @@
 //
 // The same kernel serves the dense linear (MODE 0) and the two grouped MoE GEMMs, whose
 // A rows are laid out in expert-sorted, 128-row-padded order:
-//   MODE 1 (gate_up): the B tile is 128 gate rows + the matching 128 up rows of the expert,
-//           and the tile epilogue computes silu(gate)*up in fp32 and re-quantises it to FP8
-//           with its 1x128 scale straight from the accumulators (no 16-bit round trip);
+//   MODE 1 (gate_up): the B tile interleaves 64-row chunks of the expert's gate and up rows
+//           (gate[0,64) | up[0,64) | gate[64,128) | up[64,128) of one 128-wide output group), so
+//           every promotion thread holds gate AND up of the same 64 columns; the tile epilogue
+//           computes silu(gate)*up in fp32 and re-quantises it to FP8 with its 1x128 scale
+//           straight from the accumulators (no 16-bit round trip, no exchange of operands);
 //   MODE 2 (down): rows are scattered to their (token, slot) position, times the router weight.
 #pragma once
 
@@ -77,7 +79,7 @@ struct GemmCfg {
   // 12 warps start with 168 registers each (3 warps per sub-partition); the promotion warps,
   // which hold 128 accumulators + 64 staged TMEM values, then grow to 224 with setmaxnreg
   // while the producer / MMA warpgroup shrinks to 56 (2*224 + 56 = 504 <= 512 per sub-partition).
-  static constexpr int kExchangeBytes = 64 * kBM * 4;  // MODE 1: 64 columns x 128 rows of fp32
+  static constexpr int kExchangeBytes = 2 * kBM * 4;  // MODE 1: partial row amax of the two column halves
 };
 
 // Shared-memory plan of one instantiation. The promotion warps stage their part of the output
@@ -97,6 +99,7 @@ struct GemmLayout {
   static constexpr int kStoreWarps = MODE == GEMM_GROUPED_SILU_QUANT ? 4 : Cfg::kEpiWarps;
   static constexpr int kStagingBytes =
       (MODE == GEMM_GROUPED_SILU_QUANT ? Cfg::kExchangeBytes : 0) + (kStaged ? kStoreWarps * kWarpStageBytes : 0);
+  static_assert(Cfg::kExchangeBytes == 1024, "row-amax exchange: two halves x 128 rows of fp32");
   static constexpr int kSmemLimit = 232448;  // 227 KB per CTA
   static constexpr int kFit = (kSmemLimit - 1024 - 256 - kStagingBytes) / (Cfg::kStageA + Cfg::kStageB);
   static constexpr int kStages = kFit > (BN == 256 ? 4 : 6) ? (BN == 256 ? 4 : 6) : kFit;
@@ -267,7 +270,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int e = p.expert_ids[mt];
         if (e < 0) continue;
         if (MODE == GEMM_GROUPED_SILU_QUANT) {
-          b_row = e * 2 * p.N + nt * 128;  // gate rows
+          b_row = e * 2 * p.N + nt * 128;  // gate rows of this 128-wide output group
           b_row2 = b_row + p.N;            // matching up rows
         } else {
           b_row += e * p.N;
@@ -280,9 +283,16 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (lane == 0) {
           ptx::mbar_expect_tx(full_bar(s), Cfg::kStageA + Cfg::kStageB);
           ptx::tma_load_2d(sA + s * Cfg::kStageA, &tmap_a, kb * kBK, mt * kBM, full_bar(s));
-          ptx::tma_load_2d(sB + s * Cfg::kStageB, &tmap_b, kb * kBK, b_row, full_bar(s));
-          if (MODE == GEMM_GROUPED_SILU_QUANT)  // B box is 128 rows in this mode: second half of the stage
-            ptx::tma_load_2d(sB + s * Cfg::kStageB + 128 * kBK, &tmap_b, kb * kBK, b_row2, full_bar(s));
+          if (MODE == GEMM_GROUPED_SILU_QUANT) {
+            // B box is 64 rows in this mode: gate lo | up lo | gate hi | up hi
+            const uint32_t d = sB + s * Cfg::kStageB;
+            ptx::tma_load_2d(d, &tmap_b, kb * kBK, b_row, full_bar(s));
+            ptx::tma_load_2d(d + 64 * kBK, &tmap_b, kb * kBK, b_row2, full_bar(s));
+            ptx::tma_load_2d(d + 128 * kBK, &tmap_b, kb * kBK, b_row + 64, full_bar(s));
+            ptx::tma_load_2d(d + 192 * kBK, &tmap_b, kb * kBK, b_row2 + 64, full_bar(s));
+          } else {
+            ptx::tma_load_2d(sB + s * Cfg::kStageB, &tmap_b, kb * kBK, b_row, full_bar(s));
+          }
         }
         __syncwarp();
       }
@@ -337,6 +347,8 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const float* as_ptr;
       const float* bs_ptr;
       float a_pf[4], b_pf[4];
+      const float* bs2_ptr;  // MODE 1: scales of the up rows (b_pf/bs_ptr are the gate rows')
+      float b2_pf[4];
     };
     auto setup = [&](int item, Item& c) -> bool {
       for (; item < total_items; item += gridDim.x) {
@@ -352,14 +364,15 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         c.item = item;
         c.row = c.mt * kBM + row_in_tile;
-        c.col0 = MODE == GEMM_GROUPED_SILU_QUANT ? c.nt * 128 : c.nt * BN + half * 128;
+        c.col0 = MODE == GEMM_GROUPED_SILU_QUANT ? c.nt * 128 + half * 64 : c.nt * BN + half * 128;
         c.row_ok = c.row < p.M;
         c.as_ptr = p.As + (int64_t)(c.row_ok ? c.row : 0) * p.as_sm;
         // row of Bs: the 128-row block of B this thread's columns come from (MODE 1: gate block
-        // nt for the first 128 TMEM columns, up block I/128 + nt for the other 128)
-        const int nb = MODE == GEMM_GROUPED_SILU_QUANT ? half * p.n_blocks + c.nt : min(c.col0 / 128, p.n_blocks - 1);
+        // nt for its first 64 TMEM columns, up block I/128 + nt for the other 64)
+        const int nb = MODE == GEMM_GROUPED_SILU_QUANT ? c.nt : min(c.col0 / 128, p.n_blocks - 1);
         const int bs_rows = MODE == GEMM_GROUPED_SILU_QUANT ? 2 * p.n_blocks : p.n_blocks;
         c.bs_ptr = p.Bs + ((int64_t)c.expert * bs_rows + nb) * num_kb;
+        c.bs2_ptr = c.bs_ptr + (int64_t)p.n_blocks * num_kb;
         c.flat = 0;
         if (MODE == GEMM_GROUPED_SCATTER) c.flat = c.row_ok ? __ldg(p.sorted_ids + c.row) : p.numel;
 #pragma unroll
@@ -367,6 +380,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const bool in = c.row_ok && c.kb0 + d < c.kb1;
           c.a_pf[d] = in ? __ldg(c.as_ptr + (int64_t)(c.kb0 + d) * p.as_sk) : 0.f;
           c.b_pf[d] = in ? __ldg(c.bs_ptr + c.kb0 + d) : 0.f;
+          if (MODE == GEMM_GROUPED_SILU_QUANT) c.b2_pf[d] = in ? __ldg(c.bs2_ptr + c.kb0 + d) : 0.f;
         }
         return true;
       }
@@ -397,10 +411,13 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (kb >= cur.kb1 || !ok) break;
           const int b = it & 1;
           const float sc = cur.a_pf[j] * cur.b_pf[j];
+          // columns 64..127 of this thread: same block scale, except the up rows of MODE 1
+          const float sc2 = MODE == GEMM_GROUPED_SILU_QUANT ? cur.a_pf[j] * cur.b2_pf[j] : sc;
           {
             const bool in = cur.row_ok && kb + 4 < cur.kb1;
             cur.a_pf[j] = in ? __ldg(cur.as_ptr + (int64_t)(kb + 4) * p.as_sk) : 0.f;
             cur.b_pf[j] = in ? __ldg(cur.bs_ptr + kb + 4) : 0.f;
+            if (MODE == GEMM_GROUPED_SILU_QUANT) cur.b2_pf[j] = in ? __ldg(cur.bs2_ptr + kb + 4) : 0.f;
           }
           ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
           if (!ok) break;
@@ -420,13 +437,13 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           promote32(acc + 32, vb, sc);
           ptx::tmem_ld_wait(va);
           ptx::tmem_ld32(ta + 96, vb);
-          promote32(acc + 64, va, sc);
+          promote32(acc + 64, va, sc2);
           ptx::tmem_ld_wait(vb);
           // every TMEM read of this buffer has landed: give it back to the MMA warp
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-          promote32(acc + 96, vb, sc);
+          promote32(acc + 96, vb, sc2);
           ++it;
         }
       }
@@ -451,6 +468,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // the bulk stores of the previous tile must have read the staging area before it is rewritten
         if (MODE != GEMM_GROUPED_SCATTER && lane == 0) ptx::tma_store_wait_read();
         __syncwarp();
+        if (MODE == GEMM_GROUPED_SILU_QUANT) named_bar_sync(2 + quarter, 64);  // the box is shared with warp ^ 4
       }
       if (MODE == GEMM_GROUPED_SILU_QUANT) {
         if (p.topk_weights != nullptr) {
@@ -461,48 +479,36 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
           for (int j = 0; j < 128; ++j) acc[j] *= w;
         }
-        // warps 4-7 hold `up`, warps 0-3 hold `gate` of the same rows and columns: hand `up`
-        // over through shared memory 64 columns at a time ([column][row]: conflict free).
+        // acc[0..64) = gate, acc[64..128) = up of output columns col0 .. col0+63; the other half of
+        // the 128-wide quantisation group lives in the warp with the same lane quarter (warp ^ 4):
+        // only the partial row amax is exchanged (pair barrier 2 + quarter, 64 threads).
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          if (half == 1) {
+        for (int j = 0; j < 64; ++j) acc[j] = silu_mul_fast(acc[j], acc[64 + j]);
+        float amax = 0.f;
 #pragma unroll
-            for (int j = 0; j < 64; ++j) exchange[j * kBM + row_in_tile] = acc[64 * r + j];
-          }
-          named_bar_sync(1, Cfg::kEpiWarps * 32);
-          if (half == 0) {
+        for (int j = 0; j < 64; ++j) amax = fmaxf(amax, fabsf(acc[j]));
+        exchange[half * kBM + row_in_tile] = amax;
+        named_bar_sync(2 + quarter, 64);
+        amax = fmaxf(fmaxf(amax, exchange[(half ^ 1) * kBM + row_in_tile]), 1e-10f);
+        const float inv = __fdividef(448.0f, amax);
 #pragma unroll
-            for (int j = 0; j < 64; ++j)
-              acc[64 * r + j] = silu_mul_fast(acc[64 * r + j], exchange[j * kBM + row_in_tile]);
-          }
-          named_bar_sync(1, Cfg::kEpiWarps * 32);
+        for (int j = 0; j < 4; ++j) {
+          float q[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) q[i] = acc[16 * j + i] * inv;  // the conversion saturates to +-448
+          uint4 v;
+          v.x = pack4_e4m3(q[0], q[1], q[2], q[3]);
+          v.y = pack4_e4m3(q[4], q[5], q[6], q[7]);
+          v.z = pack4_e4m3(q[8], q[9], q[10], q[11]);
+          v.w = pack4_e4m3(q[12], q[13], q[14], q[15]);
+          stage_chunk(half * 4 + j, v);
         }
-        if (half == 0) {
-          // this thread's 128 columns are exactly one 1x128 quantisation group
-          float amax = 0.f;
-#pragma unroll
-          for (int j = 0; j < 128; ++j) amax = fmaxf(amax, fabsf(acc[j]));
-          amax = fmaxf(amax, 1e-10f);
-          const float inv = __fdividef(448.0f, amax);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float q[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) q[i] = fminf(fmaxf(acc[16 * j + i] * inv, -448.f), 448.f);
-            uint4 v;
-            v.x = pack4_e4m3(q[0], q[1], q[2], q[3]);
-            v.y = pack4_e4m3(q[4], q[5], q[6], q[7]);
-            v.z = pack4_e4m3(q[8], q[9], q[10], q[11]);
-            v.w = pack4_e4m3(q[12], q[13], q[14], q[15]);
-            stage_chunk(j, v);
-          }
-          if (row_ok) p.q_scales[(int64_t)nt * p.q_scale_ld + row] = __fdiv_rn(amax, 448.0f);
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {  // FP8 rows [32 x 128 B] of the expert-sorted activation
-            ptx::tma_store_3d(&tmap_c, wstage, col0, cur.mt * kBM + quarter * 32, 0);
-            ptx::tma_store_commit();
-          }
+        if (half == 0 && row_ok) p.q_scales[(int64_t)nt * p.q_scale_ld + row] = __fdiv_rn(amax, 448.0f);
+        ptx::fence_proxy_async_smem();
+        named_bar_sync(2 + quarter, 64);  // both halves of the box are staged (and the amax slots are free again)
+        if (half == 0 && lane == 0) {  // FP8 rows [32 x 128 B] of the expert-sorted activation
+          ptx::tma_store_3d(&tmap_c, wstage, nt * 128, cur.mt * kBM + quarter * 32, 0);
+          ptx::tma_store_commit();
         }
       } else {
         const float w = row_weight;
