@@ -2,7 +2,8 @@
 //
 // Launch sequence (all on the caller's stream, no host sync):
 //   1 align            token->expert buckets padded to 128 rows                 (align.cu)
-//   2 gather_quant     hidden rows -> expert-sorted FP8 rows + 1x128 scales     (HBM bound)
+//   2 gather_quant     hidden rows -> expert-sorted FP8 rows + 1x128 scales     (HBM bound;
+//                      top-k >= 3: rows quantised once per token, then FP8 rows gathered)
 //   3 grouped GEMM 1   sorted rows x w1[expert]^T; the epilogue applies silu(gate)*up in fp32
 //                      and re-quantises to FP8 + 1x128 scales from the accumulators (tcgen05)
 //   4 grouped GEMM 2   x w2[expert]^T, * router weight, scattered to (token, slot)
@@ -27,7 +28,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
     const T* __restrict__ hidden, const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
     const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q, float* __restrict__ s, int chunks_per_row,
-    int64_t H, int numel, int topk, int64_t cap) {
+    int64_t H, int numel, int topk, int64_t cap, int zero_pads) {
   const int64_t slot0 = (int64_t)blockIdx.x * kGatherRows;
   if (slot0 >= *num_post_pad || expert_ids[slot0 / kMoeBlockM] < 0) return;  // uniform per block
   const int chunk = blockIdx.y * blockDim.x + threadIdx.x;
@@ -54,43 +55,65 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
 #pragma unroll
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
     amax = fmaxf(group_max<8>(amax), 1e-10f);
-    // Internal activation of the fused layer: the stored scale is the exact amax / 448, the bytes
-    // are x * (448 / amax) (one multiply per element instead of an IEEE division; the rare code
-    // that differs from x / scale by one step is far inside the layer's 1e-2 tolerance).
+    // scale = amax / 448 and q = x / scale as the reference's quantiser computes them. The quotient
+    // is formed as x * (1 / scale) plus one residual correction (rem = x - q * scale, exact in an
+    // FMA): two FMAs per element instead of an IEEE division sequence, and the same fp32 value
+    // as the division except for quotients within 2^-23 ulp of a rounding boundary. A plain
+    // reciprocal multiply is not enough for 16-bit inputs: when amax has a short mantissa many
+    // quotients sit exactly on an FP8 tie and would be broken the other way.
     const float scale = __fdiv_rn(amax, 448.0f);
-    const float inv = __fdiv_rn(448.0f, amax);
+    const float inv = __fdiv_rn(1.0f, scale);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float q0 = f[i] * inv;
+      f[i] = fmaf(fmaf(-q0, scale, f[i]), inv, q0);
+    }
     uint4 out;
-    out.x = pack4_e4m3(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-    out.y = pack4_e4m3(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-    out.z = pack4_e4m3(f[8] * inv, f[9] * inv, f[10] * inv, f[11] * inv);
-    out.w = pack4_e4m3(f[12] * inv, f[13] * inv, f[14] * inv, f[15] * inv);
-    if (active) {  // pad rows of live blocks are written as zeros so the GEMM reads defined bytes
+    out.x = pack4_e4m3(f[0], f[1], f[2], f[3]);
+    out.y = pack4_e4m3(f[4], f[5], f[6], f[7]);
+    out.z = pack4_e4m3(f[8], f[9], f[10], f[11]);
+    out.w = pack4_e4m3(f[12], f[13], f[14], f[15]);
+    // Pad rows: a GEMM output row depends on its own A row only and rows computed from pad slots
+    // are never scattered, so their content is free. Zeros keep the tensor cores' power draw
+    // down when tiles are mostly real rows; with a few tokens per expert (tiles that are mostly
+    // padding, weight streaming bound) writing them would dominate this kernel, so they are skipped.
+    if (active && (zero_pads || flat[r] < numel)) {
       *reinterpret_cast<uint4*>(q + (slot0 + r) * H + chunk * 16) = out;
       if ((threadIdx.x & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot0 + r] = scale;
     }
   }
 }
 
-// Pre-quantised input (expert-parallel dispatch delivers FP8 rows + 1x128 scales): plain
-// gather of bytes and scales into the expert-sorted layout. One thread = 16 bytes of a row.
+// Pre-quantised input (rows quantised once per token by the step before, or FP8 rows + 1x128
+// scales delivered by the expert-parallel dispatch): plain gather of bytes and scales into the
+// expert-sorted layout. One thread = 16 bytes of kGatherRows consecutive sorted rows; indices,
+// then data, of all rows are requested before any is stored.
 __global__ void __launch_bounds__(256) moe_gather_fp8_kernel(
     const uint8_t* __restrict__ hidden_q, const float* __restrict__ hidden_s, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ num_post_pad, uint8_t* __restrict__ q,
-    float* __restrict__ s, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap) {
-  const int64_t slot = blockIdx.x;
-  if (slot >= *num_post_pad || expert_ids[slot / kMoeBlockM] < 0) return;
+    float* __restrict__ s, int chunks_per_row, int64_t H, int numel, int topk, int64_t cap, int zero_pads) {
+  const int64_t slot0 = (int64_t)blockIdx.x * kGatherRows;
+  if (slot0 >= *num_post_pad || expert_ids[slot0 / kMoeBlockM] < 0) return;  // uniform per block
   const int chunk = blockIdx.y * blockDim.x + threadIdx.x;
   if (chunk >= chunks_per_row) return;
-  const int flat = sorted_ids[slot];
-  uint4 v = make_uint4(0, 0, 0, 0);
-  float sc = 0.f;
-  if (flat < numel) {
-    const int64_t tok = flat / topk;
-    v = ld_nc_16(hidden_q + tok * H + chunk * 16);
-    if ((chunk & 7) == 0) sc = __ldg(hidden_s + tok * (H / 128) + chunk / 8);
+  int flat[kGatherRows];
+#pragma unroll
+  for (int r = 0; r < kGatherRows; ++r) flat[r] = __ldg(sorted_ids + slot0 + r);
+  uint4 v[kGatherRows];
+  float sc[kGatherRows];
+#pragma unroll
+  for (int r = 0; r < kGatherRows; ++r) {
+    const bool real = flat[r] < numel;
+    const int64_t tok = real ? flat[r] / topk : 0;
+    v[r] = real ? ld_nc_16(hidden_q + tok * H + chunk * 16) : make_uint4(0, 0, 0, 0);
+    sc[r] = real && (chunk & 7) == 0 ? __ldg(hidden_s + tok * (H / 128) + chunk / 8) : 0.f;
   }
-  *reinterpret_cast<uint4*>(q + slot * H + chunk * 16) = v;
-  if ((chunk & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot] = sc;
+#pragma unroll
+  for (int r = 0; r < kGatherRows; ++r) {
+    if (!zero_pads && flat[r] >= numel) continue;  // see moe_gather_quant_kernel
+    *reinterpret_cast<uint4*>(q + (slot0 + r) * H + chunk * 16) = v[r];
+    if ((chunk & 7) == 0) s[(int64_t)(chunk / 8) * cap + slot0 + r] = sc[r];
+  }
 }
 
 // out[t, :] = scale * sum_j y[t*topk + j, :] over the slots whose expert id is valid.
@@ -121,10 +144,62 @@ __global__ void __launch_bounds__(256) moe_sum_reduce_kernel(const T* __restrict
   *reinterpret_cast<uint4*>(out + t * H + v * 8) = o;
 }
 
+// Same reduction over fp32 split-K partials y[splits][rows * slots][H] of the down GEMM
+// (few-token case): out[r, :] = scale * sum over valid slots j and splits s. Rows whose slots
+// are all invalid come out as zeros.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_sum_reduce_splits_kernel(const float* __restrict__ y,
+                                                                    const int32_t* __restrict__ topk_ids,
+                                                                    T* __restrict__ out, int64_t rows, int slots,
+                                                                    int splits, int64_t split_stride, int E, int64_t H,
+                                                                    float scale) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vec_per_row = (int)(H / 8);
+  if (c >= rows * vec_per_row) return;
+  const int64_t r = c / vec_per_row;
+  const int v = (int)(c - r * vec_per_row);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int j = 0; j < slots; ++j) {
+    const int e = topk_ids[r * slots + j];
+    if (e < 0 || e >= E) continue;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float* src = y + sp * split_stride + (r * slots + j) * H + v * 8;
+      const uint4 a = ld_nc_16(src), b = ld_nc_16(src + 4);
+      acc[0] += __uint_as_float(a.x); acc[1] += __uint_as_float(a.y);
+      acc[2] += __uint_as_float(a.z); acc[3] += __uint_as_float(a.w);
+      acc[4] += __uint_as_float(b.x); acc[5] += __uint_as_float(b.y);
+      acc[6] += __uint_as_float(b.z); acc[7] += __uint_as_float(b.w);
+    }
+  }
+  uint4 o;
+  T* oh = reinterpret_cast<T*>(&o);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * scale);
+  *reinterpret_cast<uint4*>(out + r * H + v * 8) = o;
+}
+
+// Split-K factor of the down GEMM. With a handful of tokens the live tiles (about one 128-row
+// tile per routed expert, H/256 column tiles each) leave most SMs without weights to stream;
+// K = I is then split and the fp32 partials are summed by the slot reduction.
+static int moe_down_k_splits(int64_t numel, int E, int64_t H, int64_t I, int sms) {
+  const int64_t live = (numel < E ? numel : E) + numel / kMoeBlockM;
+  const int64_t tiles = live * cdiv(H, 256);
+  const int64_t num_kb = I / 128;
+  if (tiles * 4 >= (int64_t)sms * 3 || num_kb < 8) return 1;
+  int64_t s = sms / tiles;
+  if (s > num_kb / 4) s = num_kb / 4;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : (int)s;
+}
+
 struct MoeWorkspace {
   int64_t cap;  // rows of the expert-sorted layout (multiple of 128)
   int64_t cap_blocks;
-  size_t off_sorted, off_expert, off_npp, off_cumsum, off_align, off_aq1, off_as1, off_aq2, off_as2, off_c3, total;
+  int down_splits;  // > 1: the down GEMM writes fp32 split-K partials instead of 16-bit rows
+  bool quant_first;  // quantise the T input rows once, then gather FP8 rows (instead of quantising every pair)
+  size_t off_sorted, off_expert, off_npp, off_cumsum, off_align, off_aq1, off_as1, off_aq2, off_as2, off_c3, off_xq, off_xs, total;
 };
 
 static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, int64_t I) {
@@ -144,7 +219,13 @@ static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, 
   w.off_as1 = take((size_t)w.cap * (H / 128) * 4);
   w.off_aq2 = take((size_t)w.cap * I);
   w.off_as2 = take((size_t)w.cap * (I / 128) * 4);
-  w.off_c3 = take((size_t)numel * H * 2);
+  w.down_splits = moe_down_k_splits(numel, E, H, I, sm_count());
+  w.off_c3 = take(w.down_splits > 1 ? (size_t)w.down_splits * numel * H * 4 : (size_t)numel * H * 2);
+  // Each token's row is used by topk pairs: from three slots up, quantising it once and moving
+  // FP8 bytes moves fewer bytes than re-reading the 16-bit row per pair.
+  w.quant_first = topk >= 3;
+  w.off_xq = take(w.quant_first ? (size_t)T * H : 0);
+  w.off_xs = take(w.quant_first ? (size_t)T * (H / 128) * 4 : 0);
   w.total = o;
   return w;
 }
@@ -164,13 +245,17 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   float* as1 = reinterpret_cast<float*>(ws + L.off_as1);
   uint8_t* aq2 = ws + L.off_aq2;
   float* as2 = reinterpret_cast<float*>(ws + L.off_as2);
-  T* c3 = no_combine ? static_cast<T*>(out) : reinterpret_cast<T*>(ws + L.off_c3);
+  int down_splits = L.down_splits;
+  if (const char* e = getenv("B200_MOE_DOWN_SPLITK"))  // tuning hook: 0 keeps the 16-bit single-pass path
+    if (atoi(e) == 0) down_splits = 1;
+  const bool split = down_splits > 1;
+  T* c3 = no_combine && !split ? static_cast<T*>(out) : reinterpret_cast<T*>(ws + L.off_c3);
 
   int rc = b200_moe_align_block_size(topk_ids, B200_I32, numel, E + 1, kMoeBlockM, sorted, L.cap, expert_ids,
                                      L.cap_blocks, npp, cumsum, 1, ws + L.off_align,
                                      b200_moe_align_workspace_bytes(numel, E + 1), st);
   if (rc) return rc;
-  if (no_combine) {
+  if (no_combine && !split) {
     // rows of slots whose expert is not on this rank are never written by GEMM 2
     cudaError_t e = cudaMemsetAsync(out, 0, (size_t)numel * H * sizeof(T), st);
     if (e != cudaSuccess) {
@@ -179,16 +264,28 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
     }
   }
   {
+    const uint8_t* hq = static_cast<const uint8_t*>(hidden);
+    const float* hs = hidden_scale;
+    if (hs == nullptr && L.quant_first) {
+      uint8_t* xq = ws + L.off_xq;
+      float* xs = reinterpret_cast<float*>(ws + L.off_xs);
+      rc = b200_per_token_group_quant_fp8(hidden, std::is_same<T, __half>::value ? B200_F16 : B200_BF16, xq, xs, T_tokens,
+                                          H, 128, H / 128, 1, 1e-10f, B200_QUANT_DIV, st);
+      if (rc) return rc;
+      hq = xq;
+      hs = xs;
+    }
     const int cpr = (int)(H / 16);
     const int threads = cpr < 256 ? (cpr + 31) / 32 * 32 : 256;  // whole warps; cpr is a multiple of 8
-    dim3 grid((unsigned)L.cap, (unsigned)cdiv(cpr, threads));
-    if (hidden_scale == nullptr) grid.x = (unsigned)(L.cap / kGatherRows);
-    if (hidden_scale != nullptr)
-      moe_gather_fp8_kernel<<<grid, threads, 0, st>>>(static_cast<const uint8_t*>(hidden), hidden_scale, sorted,
-                                                     expert_ids, npp, aq1, as1, cpr, H, (int)numel, topk, L.cap);
+    dim3 grid((unsigned)(L.cap / kGatherRows), (unsigned)cdiv(cpr, threads));
+    int zero_pads = numel >= (int64_t)E * 32;  // on average a quarter of a tile per expert or more
+    if (const char* e = getenv("B200_MOE_ZERO_PADS")) zero_pads = atoi(e);  // tuning hook
+    if (hs != nullptr)
+      moe_gather_fp8_kernel<<<grid, threads, 0, st>>>(hq, hs, sorted, expert_ids, npp, aq1, as1, cpr, H, (int)numel, topk,
+                                                     L.cap, zero_pads);
     else
       moe_gather_quant_kernel<T><<<grid, threads, 0, st>>>(static_cast<const T*>(hidden), sorted, expert_ids, npp, aq1,
-                                                          as1, cpr, H, (int)numel, topk, L.cap);
+                                                          as1, cpr, H, (int)numel, topk, L.cap, zero_pads);
     if ((rc = check_launch("moe_gather"))) return rc;
   }
   int force_bn = 0;
@@ -206,6 +303,17 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   // GEMM 2: [cap, I] x w2[E, H, I]^T -> rows scattered to (token, slot), times the router weight
   p.As = as2; p.as_sk = L.cap; p.Bs = w2_scale; p.C = c3; p.ldc = H; p.N = (int)H; p.K = (int)I;
   p.topk_weights = weight_on_input ? nullptr : topk_weights;
+  if (split) {
+    p.split_stride = numel * H;
+    if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, float>(aq2, w2, (int64_t)E * H, p, 256, st, tiles_hint, down_splits)))
+      return rc;
+    const int64_t rows = no_combine ? numel : T_tokens;
+    const int64_t total = rows * (H / 8);
+    moe_sum_reduce_splits_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
+        reinterpret_cast<const float*>(c3), topk_ids, static_cast<T*>(out), rows, no_combine ? 1 : topk, down_splits,
+        numel * H, E, H, no_combine ? 1.0f : routed_scale);
+    return check_launch("moe_sum_reduce_splits");
+  }
   if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, T>(aq2, w2, (int64_t)E * H, p, force_bn, st, tiles_hint))) return rc;
   if (!no_combine) {
     const int64_t total = T_tokens * (H / 8);

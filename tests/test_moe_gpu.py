@@ -68,6 +68,29 @@ def test_shapes_vs_fp32_oracle(T, E, topk, H, I):
     assert O.rel_frobenius(out.float().cpu(), ref) < TOL
 
 
+@pytest.mark.parametrize("T,E,topk,H,I", [(1, 8, 2, 256, 2048), (3, 8, 2, 512, 1024), (5, 16, 4, 256, 1536)])
+def test_few_tokens_split_k_down_gemm(T, E, topk, H, I):
+    """A handful of tokens: the down GEMM splits K = I over the SMs and the slot reduction sums
+    the fp32 partials; with and without the slot reduction, and with ids of other ranks (-1)."""
+    g = torch.Generator().manual_seed(100 + T)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 40 + T)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), topk, True)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti, routed_scaling_factor=1.5)
+    assert O.rel_frobenius(out.float().cpu(), ref * 1.5) < TOL
+    nc = _run(x, w1, w2, w1_s, w2_s, tw, ti, no_combine=True)
+    ref_nc = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128], no_combine=True)
+    assert O.rel_frobenius(nc.float().cpu(), ref_nc) < TOL
+    local = ti.clone()
+    local[:, 0] = -1  # first slot of every token lives on another rank
+    part = _run(x, w1, w2, w1_s, w2_s, tw, local)
+    ref_part = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, local, [128, 128])
+    assert O.rel_frobenius(part.float().cpu(), ref_part) < TOL
+    nc_part = _run(x, w1, w2, w1_s, w2_s, tw, local, no_combine=True)
+    assert nc_part[:, 0].abs().max().item() == 0
+
+
 def test_expert_parallel_minus_one_ids_sum_to_full_result():
     T, E, topk, H, I = 96, 16, 4, 512, 256
     g = torch.Generator().manual_seed(11)
