@@ -144,6 +144,30 @@ int b200_fused_experts_fp8(const void* hidden, const float* hidden_scale, int h_
                            int apply_router_weight_on_input, float routed_scaling_factor,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Expert routing (the step before fused_experts): scores -> top-k weights and expert ids
+ * replaces: python/sglang/srt/layers/moe/topk.py:550-588 (fused_topk_torch_native) and :640-700
+ *           (fused_topk -> sgl-kernel topk_softmax / topk_sigmoid,
+ *            sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu, moe_topk_sigmoid_kernels.cu);
+ *           topk.py:703-764 (grouped_topk_gpu) and :923-992 (biased_grouped_topk_impl ->
+ *            sgl-kernel/csrc/moe/moe_fused_gate.cu)
+ * logits [T,E] f32/bf16/f16 row-major; correction_bias fp32 [E] or NULL.
+ * scores = softmax(row) or sigmoid(element) in fp32; selection compares scores + bias;
+ * n_group > 1: experts form n_group equal consecutive groups, a group's score is the maximum
+ * (B200_GROUP_MAX) or the sum of the two largest (B200_GROUP_TOP2_SUM) of its selection values,
+ * only the topk_group best groups stay eligible. Ties go to the lower index (the rule of the
+ * reference's CUDA kernels, moe_topk_softmax_kernels.cu:545-546). Outputs, in descending order
+ * of the selection value: topk_weights fp32 [T,topk] = unbiased scores of the chosen experts,
+ * divided by their sum when renormalize != 0, then times output_scale (pass 1.0f for none);
+ * topk_ids int32 [T,topk]. Rows t >= *num_token_non_padded (device scalar, may be NULL) get
+ * id -1 (topk.py:999-1016). Limits: E <= 1024, topk <= 32, n_group <= 32. No workspace. */
+enum { B200_SCORE_SOFTMAX = 0, B200_SCORE_SIGMOID = 1 };
+enum { B200_GROUP_MAX = 0, B200_GROUP_TOP2_SUM = 1 };
+int b200_route_topk(const void* logits, int logits_dtype, const float* correction_bias, int64_t T,
+                    int E, int topk, int scoring, int n_group, int topk_group, int group_score,
+                    int renormalize, float output_scale, const int32_t* num_token_non_padded,
+                    float* topk_weights, int32_t* topk_ids, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

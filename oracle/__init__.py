@@ -8,6 +8,10 @@ Parity status: PINNED. Every function in ``oracle.block_fp8`` is compared
 bit-for-bit (integer / byte outputs) or to float equality with the reference's
 own torch-native functions in ``tests/golden/make_golden.py`` (run where the
 reference tree is importable); the resulting vectors are committed under
-``tests/golden/`` and re-checked by the CPU test-suite.
+``tests/golden/`` and re-checked by the CPU test-suite. One deliberate difference: where
+the reference calls ``torch.topk(..., sorted=False)`` (order of the k results and ties
+unspecified) the routing functions here return descending order with the lower index first
+on ties, the rule of the reference's CUDA routing kernels; those vectors are compared by
+expert id.
 """
 from .block_fp8 import *  # noqa: F401,F403

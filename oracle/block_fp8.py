@@ -55,6 +55,9 @@ __all__ = [
     "fused_experts_fp8",
     "softmax_topk",
     "biased_grouped_topk",
+    "sigmoid_topk",
+    "grouped_topk",
+    "canonical_routing",
     "ep_local_expert_ids",
     "rel_frobenius",
 ]
@@ -272,9 +275,17 @@ def fused_experts_fp8(
 
 
 # ------------------------------------------------------------------------- routing
+def _topk(x: torch.Tensor, k: int):
+    """``torch.topk`` with the tie rule pinned: equal values go to the lower index (what the
+    reference's CUDA kernels do, sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:545-546;
+    ``torch.topk`` itself leaves ties unspecified). Results in descending order."""
+    v, i = torch.sort(x, dim=-1, descending=True, stable=True)
+    return v[..., :k], i[..., :k]
+
+
 def softmax_topk(logits: torch.Tensor, topk: int, renormalize: bool = True):
     w = logits.float().softmax(dim=-1)
-    w, ids = torch.topk(w, topk, dim=-1)
+    w, ids = _topk(w, topk)
     if renormalize:
         w = w / w.sum(dim=-1, keepdim=True)
     return w, ids.to(torch.int32)
@@ -296,18 +307,58 @@ def biased_grouped_topk(
     T, E = scores.shape
     sfc = scores + correction_bias.float().unsqueeze(0)
     group_scores = sfc.view(T, num_expert_group, -1).topk(2, dim=-1)[0].sum(dim=-1)
-    group_idx = torch.topk(group_scores, k=topk_group, dim=-1, sorted=False)[1]
+    group_idx = _topk(group_scores, topk_group)[1]
     group_mask = torch.zeros_like(group_scores)
     group_mask.scatter_(1, group_idx, 1)
     score_mask = group_mask.unsqueeze(-1).expand(T, num_expert_group, E // num_expert_group).reshape(T, -1)
     tmp = sfc.masked_fill(~score_mask.bool(), float("-inf"))
-    ids = torch.topk(tmp, k=topk, dim=-1, sorted=False)[1]
+    ids = _topk(tmp, topk)[1]
     w = scores.gather(1, ids)
     if renormalize:
         w = w / w.sum(dim=-1, keepdim=True)
     if routed_scaling_factor is not None:
         w = w * routed_scaling_factor
     return w.to(torch.float32), ids.to(torch.int32)
+
+
+def sigmoid_topk(logits: torch.Tensor, topk: int, renormalize: bool = True,
+                 correction_bias: Optional[torch.Tensor] = None):
+    """Sigmoid scores, selection on ``scores + correction_bias``, weights are the unbiased
+    scores (python/sglang/srt/layers/moe/topk.py:550-588 with scoring_func="sigmoid")."""
+    scores = logits.float().sigmoid()
+    if correction_bias is not None:
+        ids = _topk(scores + correction_bias.float().unsqueeze(0), topk)[1]
+        w = scores.gather(1, ids)
+    else:
+        w, ids = _topk(scores, topk)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
+def grouped_topk(logits: torch.Tensor, topk: int, num_expert_group: int, topk_group: int,
+                 renormalize: bool = True):
+    """Softmax scores; a group's score is its maximum; experts outside the ``topk_group`` best
+    groups are zeroed; top-k of what is left (python/sglang/srt/layers/moe/topk.py:703-764)."""
+    scores = torch.softmax(logits.float(), dim=-1)
+    T, E = scores.shape
+    group_scores = scores.view(T, num_expert_group, -1).max(dim=-1).values
+    group_idx = _topk(group_scores, topk_group)[1]
+    group_mask = torch.zeros_like(group_scores)
+    group_mask.scatter_(1, group_idx, 1)
+    score_mask = group_mask.unsqueeze(-1).expand(T, num_expert_group, E // num_expert_group).reshape(T, -1)
+    tmp = scores.masked_fill(~score_mask.bool(), 0.0)
+    w, ids = _topk(tmp, topk)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
+def canonical_routing(w: torch.Tensor, ids: torch.Tensor):
+    """Rows reordered by expert id: the reference leaves the order of the k results unspecified
+    (``sorted=False``), so two correct routings are compared in this form."""
+    order = torch.argsort(ids.long(), dim=-1, stable=True)
+    return w.gather(1, order), ids.gather(1, order)
 
 
 def ep_local_expert_ids(topk_ids: torch.Tensor, num_experts: int, ep_size: int, ep_rank: int):

@@ -13,3 +13,13 @@ from .moe_align_block_size import moe_align_block_size, sgl_moe_align_block_size
 
 __version__ = "0.1.0"
 from .fused_moe import MoeRunnerConfig, StandardTopKOutput, fused_experts, fused_moe  # noqa: F401,E402
+from .topk import (  # noqa: F401,E402
+    TopKConfig,
+    biased_grouped_topk,
+    fused_topk,
+    grouped_topk,
+    moe_fused_gate,
+    select_experts,
+    topk_sigmoid,
+    topk_softmax,
+)

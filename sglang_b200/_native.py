@@ -48,6 +48,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
          c_int, c_int, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_size_t, c_void_p],
     ),
+    "b200_route_topk": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+         c_void_p, c_void_p, c_void_p],
+    ),
 }
 
 BF16, F16, F32, I32, I64 = 0, 1, 2, 3, 4

@@ -1,16 +1,117 @@
-"""Routing that feeds ``fused_experts``: softmax / sigmoid top-k and DeepSeek-style biased
-grouped top-k, with the reference's function names and argument order
-(python/sglang/srt/layers/moe/topk.py: ``fused_topk_torch_native`` :550-588,
-``biased_grouped_topk_impl`` :923-992). This is the step BEFORE the hot path; it is stated
-here in torch ops on the tensors' own device so that benchmarks and callers can produce
-``(topk_weights fp32, topk_ids int32)`` without the reference installed."""
+"""Expert routing that feeds ``fused_experts``: softmax / sigmoid top-k, grouped top-k and the
+DeepSeek-style biased grouped top-k, with the reference's function names and argument order
+(python/sglang/srt/layers/moe/topk.py: ``fused_topk`` :640-700, ``grouped_topk_gpu`` :703-764,
+``biased_grouped_topk_impl`` :923-992, ``select_experts`` :1355-1500; sgl-kernel's in-place
+``topk_softmax`` / ``topk_sigmoid`` / ``moe_fused_gate``). One hand-written warp-per-token CUDA
+kernel behind ``b200_route_topk`` computes all of them; CUDA tensors only, no fallback.
+
+Ties go to the lower expert index and results come in descending order of the selection value
+(the reference's ``sorted=False`` calls leave the order unspecified)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Optional, Tuple
 
 import torch
 
+from . import _native as N
 
+SOFTMAX, SIGMOID = 0, 1
+GROUP_MAX, GROUP_TOP2_SUM = 0, 1
+
+
+def _route(
+    gating_output: torch.Tensor,
+    topk: int,
+    renormalize: bool,
+    scoring: int,
+    correction_bias: Optional[torch.Tensor] = None,
+    num_expert_group: int = 0,
+    topk_group: int = 0,
+    group_score: int = GROUP_MAX,
+    output_scale: float = 1.0,
+    num_token_non_padded: Optional[torch.Tensor] = None,
+    topk_weights: Optional[torch.Tensor] = None,
+    topk_ids: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    assert gating_output.dim() == 2, "gating_output must be [num_tokens, num_experts]"
+    N.require_cuda(gating_output)
+    assert gating_output.dtype in (torch.float32, torch.bfloat16, torch.float16), "unsupported logits dtype"
+    logits = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
+    T, E = logits.shape
+    dev = logits.device
+    if topk_weights is None:
+        topk_weights = torch.empty(T, topk, dtype=torch.float32, device=dev)
+    if topk_ids is None:
+        topk_ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    assert topk_weights.dtype == torch.float32 and topk_ids.dtype == torch.int32
+    assert topk_weights.is_contiguous() and topk_ids.is_contiguous()
+    assert tuple(topk_weights.shape) == (T, topk) and tuple(topk_ids.shape) == (T, topk)
+    bias = None
+    if correction_bias is not None:
+        assert correction_bias.numel() == E, "correction_bias must have one entry per expert"
+        bias = correction_bias.to(device=dev, dtype=torch.float32).contiguous()
+    nvalid = None
+    if num_token_non_padded is not None:
+        nvalid = num_token_non_padded.to(device=dev, dtype=torch.int32).reshape(1)
+    if T == 0:
+        return topk_weights, topk_ids
+    with N.on_device(logits):
+        st = N.load().b200_route_topk(
+            N.ptr(logits), N.DTYPE_CODE[logits.dtype], N.ptr(bias), T, E, topk, scoring, num_expert_group or 0,
+            topk_group or 0, group_score, int(bool(renormalize)), float(output_scale), N.ptr(nvalid),
+            N.ptr(topk_weights), N.ptr(topk_ids), N.current_stream(),
+        )
+    N.check(st, "route_topk")
+    return topk_weights, topk_ids
+
+
+def _scoring_code(scoring_func: str) -> int:
+    if scoring_func == "softmax":
+        return SOFTMAX
+    if scoring_func == "sigmoid":
+        return SIGMOID
+    raise ValueError(f"Invalid scoring function: {scoring_func}")
+
+
+# ------------------------------------------------------------- sgl-kernel style (in place)
+def topk_softmax(
+    topk_weights: torch.Tensor, topk_ids: torch.Tensor, gating_output: torch.Tensor, renormalize: bool = False
+) -> None:
+    """sgl-kernel ``topk_softmax`` (sgl-kernel/python/sgl_kernel/moe.py): fills the two outputs."""
+    _route(gating_output, topk_ids.shape[1], renormalize, SOFTMAX, topk_weights=topk_weights, topk_ids=topk_ids)
+
+
+def topk_sigmoid(
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    gating_output: torch.Tensor,
+    renormalize: bool = False,
+    correction_bias: Optional[torch.Tensor] = None,
+) -> None:
+    """sgl-kernel ``topk_sigmoid``: sigmoid scores, selection on ``scores + correction_bias``."""
+    _route(gating_output, topk_ids.shape[1], renormalize, SIGMOID, correction_bias,
+           topk_weights=topk_weights, topk_ids=topk_ids)
+
+
+def moe_fused_gate(
+    input_tensor: torch.Tensor,
+    bias: torch.Tensor,
+    num_expert_group: int,
+    topk_group: int,
+    topk: int,
+    num_fused_shared_experts: int = 0,
+    routed_scaling_factor: float = 0.0,
+    apply_routed_scaling_factor_on_output: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """sgl-kernel ``moe_fused_gate``: sigmoid + bias, top-2-sum group selection, top-k, renormalised."""
+    if num_fused_shared_experts:
+        raise NotImplementedError("fused shared experts are not part of this path")
+    scale = routed_scaling_factor if apply_routed_scaling_factor_on_output else 1.0
+    return _route(input_tensor, topk, True, SIGMOID, bias, num_expert_group, topk_group, GROUP_TOP2_SUM, scale)
+
+
+# --------------------------------------------------------------------- topk.py functions
 def fused_topk(
     hidden_states: torch.Tensor,
     gating_output: torch.Tensor,
@@ -18,22 +119,34 @@ def fused_topk(
     renormalize: bool,
     correction_bias: Optional[torch.Tensor] = None,
     scoring_func: str = "softmax",
+    num_token_non_padded: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
-    if scoring_func == "softmax":
-        scores = gating_output.float().softmax(dim=-1)
-    elif scoring_func == "sigmoid":
-        scores = gating_output.float().sigmoid()
-    else:
-        raise ValueError(f"Invalid scoring function: {scoring_func}")
-    if correction_bias is not None:
-        ids = torch.topk(scores + correction_bias.unsqueeze(0), k=topk, dim=-1, sorted=False)[1]
-        w = scores.gather(1, ids)
-    else:
-        w, ids = torch.topk(scores, topk, dim=-1)
-    if renormalize:
-        w = w / w.sum(dim=-1, keepdim=True)
-    return w.to(torch.float32), ids.to(torch.int32)
+    return _route(gating_output, topk, renormalize, _scoring_code(scoring_func), correction_bias,
+                  num_token_non_padded=num_token_non_padded)
+
+
+def grouped_topk(
+    hidden_states: torch.Tensor,
+    gating_output: torch.Tensor,
+    topk: int,
+    renormalize: bool,
+    num_expert_group: Optional[int] = None,
+    topk_group: Optional[int] = None,
+    num_fused_shared_experts: int = 0,
+    routed_scaling_factor: Optional[float] = None,
+    num_token_non_padded: Optional[torch.Tensor] = None,
+    apply_routed_scaling_factor_on_output: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax scores, a group's score is its maximum (DeepSeek-V2 routing)."""
+    assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
+    if num_fused_shared_experts:
+        raise NotImplementedError("fused shared experts are not part of this path")
+    scale = 1.0
+    if renormalize and apply_routed_scaling_factor_on_output and routed_scaling_factor is not None:
+        scale = routed_scaling_factor
+    return _route(gating_output, topk, renormalize, SOFTMAX, None, num_expert_group, topk_group, GROUP_MAX, scale,
+                  num_token_non_padded)
 
 
 def biased_grouped_topk(
@@ -42,28 +155,65 @@ def biased_grouped_topk(
     correction_bias: torch.Tensor,
     topk: int,
     renormalize: bool,
-    num_expert_group: int,
-    topk_group: int,
+    num_expert_group: Optional[int] = None,
+    topk_group: Optional[int] = None,
+    num_fused_shared_experts: int = 0,
     routed_scaling_factor: Optional[float] = None,
+    num_token_non_padded: Optional[torch.Tensor] = None,
     apply_routed_scaling_factor_on_output: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sigmoid scores; a group's score is the sum of its two best biased scores; keep
     ``topk_group`` groups; take the top-k biased scores among them; weights are the unbiased
-    scores, renormalised."""
+    scores, renormalised (DeepSeek-V3 routing)."""
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
-    scores = gating_output.float().sigmoid()
-    T, E = scores.shape
-    sfc = scores + correction_bias.float().unsqueeze(0)
-    group_scores = sfc.view(T, num_expert_group, -1).topk(2, dim=-1)[0].sum(dim=-1)
-    group_idx = torch.topk(group_scores, k=topk_group, dim=-1, sorted=False)[1]
-    group_mask = torch.zeros_like(group_scores)
-    group_mask.scatter_(1, group_idx, 1)
-    score_mask = group_mask.unsqueeze(-1).expand(T, num_expert_group, E // num_expert_group).reshape(T, -1)
-    tmp = sfc.masked_fill(~score_mask.bool(), float("-inf"))
-    ids = torch.topk(tmp, k=topk, dim=-1, sorted=False)[1]
-    w = scores.gather(1, ids)
-    if renormalize:
-        w = w / w.sum(dim=-1, keepdim=True)
-        if apply_routed_scaling_factor_on_output and routed_scaling_factor is not None:
-            w = w * routed_scaling_factor
-    return w.to(torch.float32), ids.to(torch.int32)
+    if num_fused_shared_experts:
+        raise NotImplementedError("fused shared experts are not part of this path")
+    scale = 1.0
+    if renormalize and apply_routed_scaling_factor_on_output and routed_scaling_factor is not None:
+        scale = routed_scaling_factor
+    return _route(gating_output, topk, renormalize, SIGMOID, correction_bias, num_expert_group, topk_group,
+                  GROUP_TOP2_SUM, scale, num_token_non_padded)
+
+
+@dataclass
+class TopKConfig:
+    """The routing knobs of the reference's ``TopKConfig`` (topk.py:199-214) this path reads."""
+
+    top_k: int
+    use_grouped_topk: bool = False
+    topk_group: Optional[int] = None
+    num_expert_group: Optional[int] = None
+    renormalize: bool = True
+    num_fused_shared_experts: int = 0
+    correction_bias: Optional[torch.Tensor] = None
+    routed_scaling_factor: Optional[float] = None
+    apply_routed_scaling_factor_on_output: bool = False
+    scoring_func: str = "softmax"
+
+
+def select_experts(
+    hidden_states: torch.Tensor,
+    router_logits: torch.Tensor,
+    topk_config: TopKConfig,
+    num_token_non_padded: Optional[torch.Tensor] = None,
+):
+    """Dispatch of the reference's ``select_experts`` (topk.py:1355-1500): grouped (with or
+    without correction bias) or plain top-k; returns ``StandardTopKOutput``."""
+    from .fused_moe import StandardTopKOutput
+
+    c = topk_config
+    if c.use_grouped_topk:
+        assert c.topk_group is not None and c.num_expert_group is not None
+        if c.correction_bias is None:
+            w, ids = grouped_topk(hidden_states, router_logits, c.top_k, c.renormalize, c.num_expert_group,
+                                  c.topk_group, c.num_fused_shared_experts, c.routed_scaling_factor,
+                                  num_token_non_padded, c.apply_routed_scaling_factor_on_output)
+        else:
+            w, ids = biased_grouped_topk(hidden_states, router_logits, c.correction_bias, c.top_k, c.renormalize,
+                                         c.num_expert_group, c.topk_group, c.num_fused_shared_experts,
+                                         c.routed_scaling_factor, num_token_non_padded,
+                                         c.apply_routed_scaling_factor_on_output)
+    else:
+        w, ids = fused_topk(hidden_states, router_logits, c.top_k, c.renormalize, c.correction_bias, c.scoring_func,
+                            num_token_non_padded)
+    return StandardTopKOutput(w, ids, router_logits)

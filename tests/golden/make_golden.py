@@ -8,7 +8,7 @@ It imports the reference's torch-native functions
 (test/manual/quant/test_block_fp8.py: ``native_per_token_group_quant_fp8`` :41-66,
 ``native_w8a8_block_fp8_matmul`` :291-340, ``torch_w8a8_block_fp8_moe`` :518-547;
 python/sglang/srt/layers/moe/topk.py: ``fused_topk_torch_native`` :550-588,
-``biased_grouped_topk_impl`` :923-992; test/registered/cpu/utils.py
+``grouped_topk_gpu`` :703-764, ``biased_grouped_topk_impl`` :923-992; test/registered/cpu/utils.py
 ``convert_weight`` :53-101), runs them on small seeded inputs built the way the
 reference's tests build theirs, asserts that ``oracle/`` reproduces every output
 exactly, and stores inputs + outputs as ``.npz`` (FP8 and bf16 tensors are stored as
@@ -171,6 +171,14 @@ def main():
     print("moe ok")
 
     # ---- routing
+    def same_routing(rw, ri, ow, oi):
+        # the reference's sorted=False calls leave the order of the k results unspecified; the
+        # oracle pins it (descending, lower index first on ties): compare by expert id
+        rw, ri = O.canonical_routing(rw, ri)
+        ow, oi = O.canonical_routing(ow, oi)
+        assert torch.equal(ri, oi)
+        torch.testing.assert_close(rw, ow, rtol=1e-6, atol=0)
+
     out = {}
     torch.manual_seed(0)
     logits = torch.randn(17, 8)
@@ -184,8 +192,23 @@ def main():
     bias = torch.randn(256) * 0.01
     rw, ri = impl(torch.zeros(19, 4), logits, bias, 8, True, 8, 4)
     ow, oi = O.biased_grouped_topk(logits, bias, 8, 8, 4, True)
-    assert torch.equal(rw, ow) and torch.equal(ri, oi)
+    same_routing(rw, ri, ow, oi)
     out["grouped/logits"], out["grouped/bias"], out["grouped/w"], out["grouped/ids"] = raw(logits), raw(bias), raw(rw), raw(ri)
+    # sigmoid scores with a correction bias, no groups (fused_topk_torch_native :550-588)
+    logits = torch.randn(23, 64)
+    bias = torch.randn(64) * 0.05
+    rw, ri = RT.fused_topk_torch_native(torch.zeros(23, 4), logits, 6, True, correction_bias=bias, scoring_func="sigmoid")
+    ow, oi = O.sigmoid_topk(logits, 6, True, bias)
+    same_routing(rw, ri.to(torch.int32), ow, oi)
+    out["sigmoid/logits"], out["sigmoid/bias"], out["sigmoid/w"], out["sigmoid/ids"] = raw(logits), raw(bias), raw(rw), raw(ri.to(torch.int32))
+    # softmax scores, group score = maximum (grouped_topk_gpu :703-764; DeepSeek-V2 shape: 160 experts, 8 groups)
+    impl = RT.grouped_topk_gpu
+    impl = getattr(impl, "_torchdynamo_orig_callable", None) or getattr(impl, "__wrapped__", impl)
+    logits = torch.randn(21, 160)
+    rw, ri = impl(torch.zeros(21, 4), logits, 6, True, 8, 3)
+    ow, oi = O.grouped_topk(logits, 6, 8, 3, True)
+    same_routing(rw, ri, ow, oi)
+    out["grouped_softmax/logits"], out["grouped_softmax/w"], out["grouped_softmax/ids"] = raw(logits), raw(rw), raw(ri)
     np.savez_compressed(os.path.join(HERE, "routing.npz"), **out)
     print("routing ok")
 

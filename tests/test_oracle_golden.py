@@ -63,13 +63,28 @@ def test_moe_matches_reference_vectors():
         assert O.rel_frobenius(out.float(), ref) < tol, name
 
 
+def _same_routing(w, ids, ref_w, ref_ids):
+    """The reference's ``sorted=False`` calls leave the order of the k results (and with it the
+    last bit of the renormalising sum) unspecified: compare by expert id, weights to 1e-6."""
+    w, ids = O.canonical_routing(w, ids)
+    ref_w, ref_ids = O.canonical_routing(ref_w, ref_ids)
+    assert torch.equal(ids, ref_ids)
+    torch.testing.assert_close(w, ref_w, rtol=1e-6, atol=0)
+
+
 def test_routing_matches_reference_vectors():
     c = load_golden("routing.npz")
     w, ids = O.softmax_topk(torch.from_numpy(c["softmax"]["logits"]), 2, True)
     assert torch.equal(w, torch.from_numpy(c["softmax"]["w"])) and torch.equal(ids, torch.from_numpy(c["softmax"]["ids"]))
     g = c["grouped"]
     w, ids = O.biased_grouped_topk(torch.from_numpy(g["logits"]), torch.from_numpy(g["bias"]), 8, 8, 4, True)
-    assert torch.equal(w, torch.from_numpy(g["w"])) and torch.equal(ids, torch.from_numpy(g["ids"]))
+    _same_routing(w, ids, torch.from_numpy(g["w"]), torch.from_numpy(g["ids"]))
+    g = c["sigmoid"]
+    w, ids = O.sigmoid_topk(torch.from_numpy(g["logits"]), 6, True, torch.from_numpy(g["bias"]))
+    _same_routing(w, ids, torch.from_numpy(g["w"]), torch.from_numpy(g["ids"]))
+    g = c["grouped_softmax"]
+    w, ids = O.grouped_topk(torch.from_numpy(g["logits"]), 6, 8, 3, True)
+    _same_routing(w, ids, torch.from_numpy(g["w"]), torch.from_numpy(g["ids"]))
 
 
 def test_align_docstring_example():
