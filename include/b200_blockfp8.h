@@ -168,6 +168,40 @@ int b200_route_topk(const void* logits, int logits_dtype, const float* correctio
                     int renormalize, float output_scale, const int32_t* num_token_non_padded,
                     float* topk_weights, int32_t* topk_ids, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Row-parallel linear with the tensor-parallel all-reduce done over peer memory
+ * replaces: python/sglang/srt/layers/linear.py:1543-1558 (RowParallelLinear.forward: GEMM, then
+ *           tensor_model_parallel_all_reduce), python/sglang/srt/distributed/communication_op.py:28-40,
+ *           sgl-kernel/csrc/allreduce/custom_all_reduce.cuh:238-383 (one-/two-shot kernels) and the
+ *           fused all-reduce + residual + RMSNorm of python/sglang/srt/layers/flashinfer_comm_fusion.py
+ * b200_w8a8_block_fp8_gemm_fanout: the block-FP8 GEMM above, but every finished tile is stored
+ * into the n_dest buffers dest[d] ([M,N] c_dtype, row-major, 16-byte aligned; `dest` is a HOST
+ * array of device pointers, which may be peer GPUs' memory mapped into this process) while the
+ * GEMM is still running. dest_by_tile != 0: the tile of 128-row block mt goes only to
+ * dest[mt % n_dest] (reduce-scatter by row block). Workspace as for the plain GEMM, sized by
+ * b200_w8a8_block_fp8_gemm_fanout_workspace_bytes.
+ * b200_allreduce_finish: n_ranks slots of slot_stride elements each (LOCAL memory; slot r holds
+ * the [M,N] partial written by rank r's fan-out GEMM; bf16/f16). Handshake with all ranks (flag arrays of 2*8 uint32, zero before the
+ * first call, epoch strictly increasing by call and identical on all ranks; my_flags local,
+ * peer_flags HOST array of every rank's flag array incl. this rank's), then
+ * sum over ranks in fp32 (+ residual -> residual_out; then * rsqrt(mean(x^2)+eps) * rms_weight
+ * when rms_weight != NULL) -> out[0]; by_tile != 0: only row blocks mt % n_ranks == rank are
+ * reduced and the results are written to out[0..n_ranks) and residual_out[0..n_ranks) (every
+ * rank's buffers; `out` and `residual_out` are HOST arrays of device pointers, NULL = none), followed
+ * by a second handshake so that on return (in stream order) every rank's output is complete.
+ * All waits are bounded (2 s); on expiry the device status word becomes 2. */
+size_t b200_w8a8_block_fp8_gemm_fanout_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int b200_w8a8_block_fp8_gemm_fanout(const void* A, const float* As, int64_t as_stride_m,
+                                    int64_t as_stride_k, const void* B, const float* Bs,
+                                    void* const* dest, int n_dest, int dest_by_tile, int c_dtype,
+                                    int64_t M, int64_t N, int64_t K, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* out, int dtype,
+                          int64_t M, int64_t N,
+                          int n_ranks, int rank, int by_tile, const void* residual,
+                          void* const* residual_out, const void* rms_weight, float eps, void* my_flags,
+                          void* const* peer_flags, uint32_t epoch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

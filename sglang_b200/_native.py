@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p, POINTER
 
 import torch
 
@@ -47,6 +47,17 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
          c_int, c_int, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_size_t, c_void_p],
+    ),
+    "b200_w8a8_block_fp8_gemm_fanout_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "b200_w8a8_block_fp8_gemm_fanout": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int64,
+         c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+    ),
+    "b200_allreduce_finish": (
+        c_int,
+        [c_void_p, c_int64, POINTER(c_void_p), c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p,
+         POINTER(c_void_p), c_void_p, c_float, c_void_p, POINTER(c_void_p), c_uint32, c_void_p],
     ),
     "b200_route_topk": (
         c_int,

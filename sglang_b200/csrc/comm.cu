@@ -1,0 +1,227 @@
+// Tensor-parallel all-reduce of the row-parallel linear, built around peer memory instead of a
+// library collective. The GEMM's epilogue has already written this rank's partial [M, N] into
+// slot `rank` of the destination ranks' slot buffers (fan-out stores over NVLink, tile by tile
+// while the GEMM runs); what is left is
+//   1. a cross-rank "partials have landed" handshake,
+//   2. out = sum over ranks of slot[r] (fp32, rank order: every rank gets the same bits),
+//      optionally + residual and RMSNorm (the reference fuses the same three steps,
+//      python/sglang/srt/layers/flashinfer_comm_fusion.py, layernorm.py forward_native),
+//   3. two-shot only: the owner of a 128-row block writes its result into every rank's output.
+// Handshakes are epoch counters in a small flag array per rank: rank r writes epoch into
+// peer[d].flags[r] with a system-scope release after a system fence, and polls its own
+// flags[0..n) with system-scope acquires. Every poll is bounded (2 s): on expiry the kernel
+// records status 2 in the device status word and returns without touching peer memory again.
+// Slots written by peers are read with L2-only loads (ld.global.cg): the L1 of this SM may
+// still hold lines of the previous call that used the same buffer.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kMaxRanks = 8;
+constexpr unsigned long long kWaitNs = 2000000000ull;
+
+struct AllReduceParams {
+  const void* slots;  // local [n_ranks][slot_stride], slot r = rank r's partial [M][N]
+  int64_t slot_stride;  // elements between slots (>= M*N)
+  void* out[kMaxRanks];       // one-shot: out[0] (local). two-shot: out[d] = rank d's output buffer
+  const void* residual;       // [M, N] or null
+  void* residual_out[kMaxRanks];  // like out: [M, N] buffers for sum + residual, or null (may alias residual)
+  const void* rms_weight;     // [N] or null
+  uint32_t* my_flags;         // local [2][kMaxRanks]
+  uint32_t* peer_flags[kMaxRanks];
+  int* status;
+  int64_t M, N;
+  int n_ranks, rank;
+  int by_tile;  // two-shot: reduce only row blocks mt % n_ranks == rank, write them to every rank
+  uint32_t epoch;
+  float eps;
+};
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Thread d < n signals rank d; returns after it has seen every rank's signal or the time limit.
+// `phase` selects the flag row. Epochs only grow, so `>=` tolerates a rank that is already a
+// call ahead.
+__device__ bool handshake(uint32_t* my_flags, uint32_t* const* peer_flags, int n, int rank, int phase, uint32_t epoch,
+                          bool signal) {
+  const int d = threadIdx.x;
+  bool ok = true;
+  if (d < n) {
+    if (signal) {
+      __threadfence_system();
+      st_release_sys(peer_flags[d] + phase * kMaxRanks + rank, epoch);
+    }
+    const unsigned long long t0 = now_ns();
+    while ((int32_t)(ld_acquire_sys(my_flags + phase * kMaxRanks + d) - epoch) < 0) {
+      if (now_ns() - t0 > kWaitNs) {
+        ok = false;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  return ok;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReduceParams p) {
+  __shared__ int s_ok;
+  __shared__ float s_red[8];
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  // block 0 announces this rank's partials; every block waits for all ranks' announcements
+  if (!handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 0, p.epoch, blockIdx.x == 0)) atomicExch(&s_ok, 0);
+  __syncthreads();
+  if (!s_ok) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+    return;
+  }
+  const int64_t N = p.N;
+  const T* slots = static_cast<const T*>(p.slots);
+  const T* residual = static_cast<const T*>(p.residual);
+  const T* w = static_cast<const T*>(p.rms_weight);
+  const int n_out = p.by_tile ? p.n_ranks : 1;
+  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
+    if (p.by_tile && (row / 128) % p.n_ranks != p.rank) continue;
+    float ss = 0.f;
+    // pass 1: sum (+ residual); with a norm the fp32 sums are parked in the first output
+    for (int64_t c = threadIdx.x * 8; c < N; c += blockDim.x * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < p.n_ranks; ++r) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (int64_t)r * p.slot_stride + row * N + c));
+        const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+      }
+      if (residual != nullptr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(residual + row * N + c);
+        const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+      }
+      uint4 o;
+      T* oh = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i]);
+      if (p.residual_out[0] != nullptr)
+        for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.residual_out[d]) + row * N + c) = o;
+      if (w == nullptr) {
+        for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += acc[i] * acc[i];
+      }
+    }
+    if (w != nullptr) {
+      // RMSNorm over the row from the unrounded fp32 sums (recomputed: the row is hot in L1/L2)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += s_red[i];
+      const float inv = rsqrtf(tot / (float)N + p.eps);
+      __syncthreads();
+      for (int64_t c = threadIdx.x * 8; c < N; c += blockDim.x * 8) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < p.n_ranks; ++r) {
+          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (int64_t)r * p.slot_stride + row * N + c));
+          const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+        }
+        if (residual != nullptr) {
+          // residual_out may alias residual: read what pass 1 stored only if it did not alias
+          const uint4 v = *reinterpret_cast<const uint4*>(residual + row * N + c);
+          const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+        }
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + c);
+        const T* wh = reinterpret_cast<const T*>(&wv);
+        uint4 o;
+        T* oh = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * inv * to_f32<T>(wh[i]));
+        for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+      }
+    }
+  }
+}
+
+// Two-shot tail: "my results are in your output" handshake (flag row 1). One block.
+__global__ void __launch_bounds__(32) allreduce_results_landed_kernel(const AllReduceParams p) {
+  const bool ok = handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 1, p.epoch, true);
+  if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+}
+
+}  // namespace b200
+
+extern "C" int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* out, int dtype, int64_t M, int64_t N, int n_ranks,
+                                     int rank, int by_tile, const void* residual, void* const* residual_out,
+                                     const void* rms_weight, float eps, void* my_flags, void* const* peer_flags,
+                                     uint32_t epoch, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(M >= 0 && N > 0 && n_ranks >= 1 && n_ranks <= kMaxRanks && rank >= 0 && rank < n_ranks,
+                 "allreduce_finish: bad shape M=%lld N=%lld ranks=%d rank=%d", (long long)M, (long long)N, n_ranks, rank);
+  if (M == 0) return B200_OK;
+  B200_CHECK_ARG(slots && out && my_flags && peer_flags, "allreduce_finish: null pointer");
+  B200_CHECK_ARG(slot_stride >= M * N && slot_stride % 8 == 0 && ((uintptr_t)slots & 15) == 0,
+                 "allreduce_finish: slot stride %lld for M*N=%lld, or unaligned slots", (long long)slot_stride,
+                 (long long)(M * N));
+  B200_UNSUPPORTED(N % 8 != 0, "allreduce_finish: N=%lld must be a multiple of 8", (long long)N);
+  B200_CHECK_ARG(dtype == B200_BF16 || dtype == B200_F16, "allreduce_finish: dtype code %d is not bf16/f16", dtype);
+  // In place (residual_out == residual) each element is read and written by the same thread in
+  // pass 1, but the norm's second pass would then read the updated value: not supported together.
+  B200_UNSUPPORTED(rms_weight != nullptr && residual != nullptr && residual_out != nullptr && residual_out[0] == residual,
+                   "allreduce_finish: an RMSNorm needs residual_out separate from residual");
+  AllReduceParams p = {};
+  p.slots = slots; p.slot_stride = slot_stride; p.residual = residual; p.rms_weight = rms_weight;
+  p.my_flags = static_cast<uint32_t*>(my_flags); p.M = M; p.N = N; p.n_ranks = n_ranks; p.rank = rank;
+  p.by_tile = by_tile != 0; p.epoch = epoch; p.eps = eps;
+  p.status = device_status_word();
+  if (!p.status) {
+    set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
+  const int n_out = p.by_tile ? n_ranks : 1;
+  for (int d = 0; d < n_out; ++d) {
+    B200_CHECK_ARG(out[d] && ((uintptr_t)out[d] & 15) == 0, "allreduce_finish: output %d null or unaligned", d);
+    p.out[d] = out[d];
+    if (residual_out != nullptr) {
+      B200_CHECK_ARG(residual_out[d] && ((uintptr_t)residual_out[d] & 15) == 0,
+                     "allreduce_finish: residual output %d null or unaligned", d);
+      p.residual_out[d] = residual_out[d];
+    }
+  }
+  for (int d = 0; d < n_ranks; ++d) {
+    B200_CHECK_ARG(peer_flags[d] != nullptr, "allreduce_finish: flag pointer %d is null", d);
+    p.peer_flags[d] = static_cast<uint32_t*>(peer_flags[d]);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int64_t want = M < (int64_t)sms * 8 ? M : (int64_t)sms * 8;
+  if (dtype == B200_BF16) allreduce_finish_kernel<__nv_bfloat16><<<(unsigned)want, 256, 0, st>>>(p);
+  else allreduce_finish_kernel<__half><<<(unsigned)want, 256, 0, st>>>(p);
+  int rc = check_launch("allreduce_finish_kernel");
+  if (rc || !p.by_tile) return rc;
+  allreduce_results_landed_kernel<<<1, 32, 0, st>>>(p);
+  return check_launch("allreduce_results_landed_kernel");
+}

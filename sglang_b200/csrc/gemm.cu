@@ -8,10 +8,17 @@
 
 namespace b200 {
 
-// C[m, n] = sum over splits of the fp32 partials; 8 elements per thread.
+// Destinations of a fan-out GEMM (see GemmParams::n_dest): n == 0 means "C only".
+struct FanOut {
+  int n, by_tile;
+  void* dest[kMaxFan];
+};
+
+// C[m, n] = sum over splits of the fp32 partials; 8 elements per thread. With a fan-out the sum
+// goes to every destination buffer (or to the owner of the 128-row block) instead of C.
 template <typename OutT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C,
-                                                            int64_t mn, int splits) {
+                                                            int64_t mn, int splits, const FanOut fan, int64_t N) {
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= mn) return;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -21,12 +28,20 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
     acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
   }
-  store8<OutT>(C + i, acc);
+  if (fan.n == 0) {
+    store8<OutT>(C + i, acc);
+    return;
+  }
+  const int d0 = fan.by_tile ? (int)((i / N / kBM) % fan.n) : 0;
+  const int d1 = fan.by_tile ? d0 + 1 : fan.n;
+  for (int d = d0; d < d1; ++d) store8<OutT>(static_cast<OutT*>(fan.dest[d]) + i, acc);
 }
 
 template <typename OutT>
-static int launch_reduce(const float* partial, void* C, int64_t mn, int splits, cudaStream_t st) {
-  splitk_reduce_kernel<OutT><<<(unsigned)cdiv(mn, 8 * 256), 256, 0, st>>>(partial, static_cast<OutT*>(C), mn, splits);
+static int launch_reduce(const float* partial, void* C, int64_t mn, int splits, cudaStream_t st,
+                         const FanOut& fan = FanOut{}, int64_t N = 1) {
+  splitk_reduce_kernel<OutT><<<(unsigned)cdiv(mn, 8 * 256), 256, 0, st>>>(partial, static_cast<OutT*>(C), mn, splits,
+                                                                         fan, N);
   return check_launch("splitk_reduce_kernel");
 }
 
@@ -45,16 +60,18 @@ extern "C" size_t b200_w8a8_block_fp8_gemm_workspace_bytes(int64_t M, int64_t N,
   return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
 
-extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m, int64_t as_stride_k,
-                                        const void* B, const float* Bs, void* C, int c_dtype, int64_t M, int64_t N,
-                                        int64_t K, void* workspace, size_t workspace_bytes, void* stream) {
-  using namespace b200;
+namespace b200 {
+static int gemm_impl(const void* A, const float* As, int64_t as_stride_m, int64_t as_stride_k, const void* B,
+                     const float* Bs, void* C, int c_dtype, int64_t M, int64_t N, int64_t K, void* workspace,
+                     size_t workspace_bytes, void* stream, const FanOut& fan) {
   B200_CHECK_ARG(M >= 0 && N >= 0 && K >= 0, "gemm: negative shape");
   if (M == 0 || N == 0) return B200_OK;
   B200_CHECK_ARG(K > 0, "gemm: K must be positive");
-  B200_CHECK_ARG(A && As && B && Bs && C, "gemm: null pointer");
+  B200_CHECK_ARG(A && As && B && Bs && (C || fan.n > 0), "gemm: null pointer");
   B200_CHECK_ARG(((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 && ((uintptr_t)C & 15) == 0,
                  "gemm: A, B and C must be 16-byte aligned");
+  for (int d = 0; d < fan.n; ++d)
+    B200_CHECK_ARG(fan.dest[d] && ((uintptr_t)fan.dest[d] & 15) == 0, "gemm: fan-out destination %d null or unaligned", d);
   B200_UNSUPPORTED(K % 16 != 0, "gemm: K=%lld must be a multiple of 16 (TMA row pitch)", (long long)K);
   B200_UNSUPPORTED(M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL, "gemm: dimension too large");
   B200_UNSUPPORTED(N % 8 != 0, "gemm: N=%lld must be a multiple of 8 (vector stores)", (long long)N);
@@ -62,6 +79,8 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
   p.As = As; p.as_sm = as_stride_m; p.as_sk = as_stride_k;
   p.Bs = Bs; p.C = C; p.ldc = N;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.n_dest = fan.n; p.dest_by_tile = fan.by_tile;
+  for (int d = 0; d < fan.n; ++d) p.dest[d] = fan.dest[d];
   int force_bn = 0;
   if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);  // test hook: 128 or 256
 
@@ -81,7 +100,7 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
     SkinnyParams sp = {};
     sp.As = As; sp.as_sm = as_stride_m; sp.as_sk = as_stride_k; sp.Bs = Bs;
     sp.M = (int)M; sp.N = (int)N; sp.K = (int)K;
-    if (splits == 1) {
+    if (splits == 1 && fan.n == 0) {
       sp.C = C;
       if (c_dtype == B200_BF16) return launch_skinny<__nv_bfloat16>(A, B, sp, 1, st);
       if (c_dtype == B200_F16) return launch_skinny<__half>(A, B, sp, 1, st);
@@ -96,9 +115,9 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
     int rc = launch_skinny<float>(A, B, sp, splits, st);
     if (rc) return rc;
     const float* part = static_cast<const float*>(workspace);
-    if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st);
-    if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st);
-    return launch_reduce<float>(part, C, M * N, splits, st);
+    if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st, fan, N);
+    if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st, fan, N);
+    return launch_reduce<float>(part, C, M * N, splits, st, fan, N);
   }
   if (splits > 1) {
     // decode-sized problem: fp32 partials per K split in the workspace, then one reduction pass
@@ -109,18 +128,19 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
     }
     p.C = workspace;
     p.split_stride = M * N;
+    p.n_dest = 0;  // the partials stay local; the reduction pass fans the sum out
     int rc = launch_gemm<GEMM_DENSE, float>(A, B, N, p, force_bn, st, 0, splits);
     if (rc) return rc;
     const float* part = static_cast<const float*>(workspace);
-    if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st);
-    if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st);
-    return launch_reduce<float>(part, C, M * N, splits, st);
+    if (c_dtype == B200_BF16) return launch_reduce<__nv_bfloat16>(part, C, M * N, splits, st, fan, N);
+    if (c_dtype == B200_F16) return launch_reduce<__half>(part, C, M * N, splits, st, fan, N);
+    return launch_reduce<float>(part, C, M * N, splits, st, fan, N);
   }
   // Large dense problems with 16-bit output: CTA pairs (each CTA loads half of the B tile)
   {
     const char* e2 = getenv("B200_GEMM_2CTA");  // hook: 0 = never, 1 = whenever legal
     const int mode2 = e2 ? atoi(e2) : -1;
-    const bool legal = c_dtype != B200_F32 && force_bn == 0 && N >= 256;
+    const bool legal = c_dtype != B200_F32 && force_bn == 0 && N >= 256 && fan.n == 0;
     const bool want = mode2 == 1 || (mode2 != 0 && kPairedByDefault && M >= 1024 && cdiv(M, 256) * cdiv(N, 256) >= 64);
     if (legal && want) {
       if (c_dtype == B200_BF16) return launch_gemm_2cta<__nv_bfloat16>(A, B, p, st);
@@ -135,4 +155,35 @@ extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t 
       set_error_detail("gemm: unknown output dtype code %d", c_dtype);
       return B200_E_BAD_ARG;
   }
+}
+}  // namespace b200
+
+extern "C" int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m, int64_t as_stride_k,
+                                        const void* B, const float* Bs, void* C, int c_dtype, int64_t M, int64_t N,
+                                        int64_t K, void* workspace, size_t workspace_bytes, void* stream) {
+  return b200::gemm_impl(A, As, as_stride_m, as_stride_k, B, Bs, C, c_dtype, M, N, K, workspace, workspace_bytes, stream,
+                         b200::FanOut{});
+}
+
+extern "C" size_t b200_w8a8_block_fp8_gemm_fanout_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const size_t plain = b200_w8a8_block_fp8_gemm_workspace_bytes(M, N, K);
+  // the decode kernel always goes through an fp32 partial when its result is fanned out
+  const size_t one = M <= b200::kSkinnyMaxM ? (size_t)M * (size_t)N * sizeof(float) : 0;
+  return plain > one ? plain : one;
+}
+
+extern "C" int b200_w8a8_block_fp8_gemm_fanout(const void* A, const float* As, int64_t as_stride_m, int64_t as_stride_k,
+                                               const void* B, const float* Bs, void* const* dest, int n_dest,
+                                               int dest_by_tile, int c_dtype, int64_t M, int64_t N, int64_t K,
+                                               void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(dest != nullptr && n_dest >= 1 && n_dest <= kMaxFan, "gemm fan-out: %d destinations (1..%d)", n_dest,
+                 kMaxFan);
+  FanOut fan = {};
+  fan.n = n_dest;
+  fan.by_tile = dest_by_tile != 0;
+  for (int d = 0; d < n_dest; ++d) fan.dest[d] = dest[d];
+  return gemm_impl(A, As, as_stride_m, as_stride_k, B, Bs, nullptr, c_dtype, M, N, K, workspace, workspace_bytes, stream,
+                   fan);
 }

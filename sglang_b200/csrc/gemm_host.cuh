@@ -99,10 +99,10 @@ inline int sm_count() {
   return sms > 0 ? sms : 148;
 }
 
-template <int BN, int MODE, typename OutT>
-inline int launch_gemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+template <int BN, int MODE, typename OutT, int FAN = 1>
+inline int launch_gemm_inst(const CUtensorMap& ta, const CUtensorMap& tb, const TmapOut<FAN>& tc, const GemmParams& p,
                             int grid, cudaStream_t st) {
-  auto k = block_fp8_gemm_kernel<BN, MODE, OutT>;
+  auto k = block_fp8_gemm_kernel<BN, MODE, OutT, FAN>;
   // per device and cheap: set on every launch rather than caching per device
   const size_t smem = GemmLayout<BN, MODE, OutT>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -151,13 +151,32 @@ inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmP
   rc = make_tmap_u8(&tb, B, (uint64_t)b_rows_total, (uint64_t)p.K,
                     MODE == GEMM_GROUPED_SILU_QUANT ? 64u : (uint32_t)bn, "B");
   if (rc) return rc;
+  if constexpr (MODE == GEMM_DENSE) {
+    if (p.n_dest > 0) {
+      // fan-out: one output map per destination buffer (unsplit only; the caller reduces split-K
+      // partials itself and fans the sum out)
+      if (p.n_dest > kMaxFan || p.k_splits != 1) {
+        set_error_detail("gemm fan-out: %d destinations, %d K splits", p.n_dest, p.k_splits);
+        return B200_E_BAD_ARG;
+      }
+      TmapOut<kMaxFan> tf;
+      for (int d = 0; d < kMaxFan; ++d) {
+        rc = make_tmap_out(&tf.m[d], p.dest[d < p.n_dest ? d : 0], 1, (uint64_t)p.M, (uint64_t)p.N, (int)sizeof(OutT),
+                           std::is_same<OutT, __nv_bfloat16>::value, "fan-out C");
+        if (rc) return rc;
+      }
+      if (bn == 256) return launch_gemm_inst<256, MODE, OutT, kMaxFan>(ta, tb, tf, p, grid, st);
+      return launch_gemm_inst<128, MODE, OutT, kMaxFan>(ta, tb, tf, p, grid, st);
+    }
+  }
   // output map: dense -> C [splits, M, N]; gate_up -> FP8 activation [cap, I]; scatter -> unused
-  CUtensorMap tc = ta;
+  TmapOut<1> tc;
+  tc.m[0] = ta;
   if (MODE == GEMM_DENSE)
-    rc = make_tmap_out(&tc, p.C, (uint64_t)p.k_splits, (uint64_t)p.M, (uint64_t)p.N, (int)sizeof(OutT),
+    rc = make_tmap_out(&tc.m[0], p.C, (uint64_t)p.k_splits, (uint64_t)p.M, (uint64_t)p.N, (int)sizeof(OutT),
                        std::is_same<OutT, __nv_bfloat16>::value, "C");
   else if (MODE == GEMM_GROUPED_SILU_QUANT)
-    rc = make_tmap_out(&tc, p.q_out, 1, (uint64_t)p.M, (uint64_t)p.N, 1, false, "q_out");
+    rc = make_tmap_out(&tc.m[0], p.q_out, 1, (uint64_t)p.M, (uint64_t)p.N, 1, false, "q_out");
   if (rc) return rc;
   if (bn == 256) return launch_gemm_inst<256, MODE, OutT>(ta, tb, tc, p, grid, st);
   if constexpr (MODE == GEMM_GROUPED_SILU_QUANT) {

@@ -59,6 +59,19 @@ struct GemmParams {
   float* q_scales;
   int64_t q_scale_ld;
   int* status;  // device status word
+  // Fan-out (dense mode, tensor-parallel row-parallel linear): n_dest > 0 sends every finished
+  // tile to the [M, N] buffers dest[0..n_dest) instead of C; they may be peer GPUs' memory (the
+  // bulk tensor stores and 16-byte stores below cross NVLink like any store). dest_by_tile != 0
+  // sends the tile of row block mt only to dest[mt % n_dest] (its owner in a reduce-scatter).
+  int n_dest, dest_by_tile;
+  void* dest[8];
+};
+
+constexpr int kMaxFan = 8;
+// Output tensor maps of one launch: one, or one per fan-out destination.
+template <int FAN>
+struct alignas(64) TmapOut {
+  CUtensorMap m[FAN];
 };
 
 constexpr int kBM = 128;
@@ -191,10 +204,11 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
   nt = r / rows;
 }
 
-template <int BN, int MODE, typename OutT>
+template <int BN, int MODE, typename OutT, int FAN = 1>
 __global__ void __launch_bounds__(GemmCfg<BN>::kThreads, 1)
 block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                      const __grid_constant__ TmapOut<FAN> tmap_out, const GemmParams p) {
+  const CUtensorMap& tmap_c = tmap_out.m[0];
   using Cfg = GemmCfg<BN>;
   using L = GemmLayout<BN, MODE, OutT>;
   constexpr int S = L::kStages;
@@ -530,7 +544,16 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               for (int bxi = 0; bxi < L::kBoxesPerWarp; ++bxi) {
                 const int bx = bxi;
                 if (col0 + bx * kColsPerBox < p.N) {
-                  ptx::tma_store_3d(&tmap_c, wstage + bx * 4096, col0 + bx * kColsPerBox, cur.mt * kBM + quarter * 32, ks);
+                  if (FAN == 1) {
+                    ptx::tma_store_3d(&tmap_c, wstage + bx * 4096, col0 + bx * kColsPerBox, cur.mt * kBM + quarter * 32, ks);
+                  } else {
+                    // the staged box goes to every destination (or to the owner of this row block)
+                    const int d0 = p.dest_by_tile ? cur.mt % p.n_dest : 0;
+                    const int d1 = p.dest_by_tile ? d0 + 1 : p.n_dest;
+                    for (int d = d0; d < d1; ++d)
+                      ptx::tma_store_3d(&tmap_out.m[d], wstage + bx * 4096, col0 + bx * kColsPerBox,
+                                        cur.mt * kBM + quarter * 32, 0);
+                  }
                 }
               }
               ptx::tma_store_commit();
@@ -560,13 +583,18 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const bool store = row_ok && (MODE != GEMM_GROUPED_SCATTER || flat < p.numel);
           if (store) {
             const int64_t out_row = MODE == GEMM_GROUPED_SCATTER ? flat : row;
-            OutT* dst = static_cast<OutT*>(p.C) + ks * p.split_stride + out_row * p.ldc + col0;
+            const int d0 = FAN > 1 && p.dest_by_tile ? cur.mt % p.n_dest : 0;
+            const int d1 = FAN == 1 ? 1 : (p.dest_by_tile ? d0 + 1 : p.n_dest);
+            for (int d = d0; d < d1; ++d) {
+              OutT* base = static_cast<OutT*>(FAN == 1 ? p.C : p.dest[d]);
+              OutT* dst = base + ks * p.split_stride + out_row * p.ldc + col0;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float t[8];
+              for (int j = 0; j < 16; ++j) {
+                float t[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) t[i] = acc[j * 8 + i] * w;
-              if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, t);
+                for (int i = 0; i < 8; ++i) t[i] = acc[j * 8 + i] * w;
+                if (col0 + j * 8 < p.N) store8<OutT>(dst + j * 8, t);
+              }
             }
           }
         }

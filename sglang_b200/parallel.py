@@ -112,11 +112,16 @@ class RowParallelLinear:
     """Block-FP8 linear whose reduction dimension is split; partial outputs are all-reduced."""
 
     def __init__(self, wq, ws, tp_rank: int, tp_size: int, bias=None, reduce_results: bool = True,
-                 input_is_parallel: bool = True, group=None):
+                 input_is_parallel: bool = True, group=None, reduce_mode: str = "nccl", max_tokens: int = 8192):
+        """``reduce_mode="peer"``: the all-reduce is fused with the GEMM over NVLink peer memory
+        (see ``peer_allreduce.PeerAllReduce``; buffers sized for ``max_tokens`` rows) instead of a
+        separate NCCL collective."""
+        assert reduce_mode in ("nccl", "peer")
         self.weight, self.weight_scale = shard_row(wq, ws, tp_rank, tp_size)
         self.bias = bias if tp_rank == 0 else None  # added once, before the sum
         self.tp_rank, self.tp_size = tp_rank, tp_size
         self.reduce_results, self.input_is_parallel, self.group = reduce_results, input_is_parallel, group
+        self.reduce_mode, self.max_tokens, self._peer = reduce_mode, max_tokens, None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from .fp8_kernel import w8a8_block_fp8_linear
@@ -124,6 +129,14 @@ class RowParallelLinear:
         if not self.input_is_parallel:
             k = x.shape[-1] // self.tp_size
             x = x[..., self.tp_rank * k : (self.tp_rank + 1) * k].contiguous()
+        if self.reduce_mode == "peer" and self.reduce_results and self.tp_size > 1 and self.bias is None:
+            from .peer_allreduce import PeerAllReduce
+
+            if self._peer is None:
+                self._peer = PeerAllReduce(self.max_tokens, self.weight.shape[0], x.dtype, self.group)
+            x2 = x.reshape(-1, x.shape[-1])
+            out, _ = self._peer.linear_bf16_input(x2, self.weight, self.weight_scale)
+            return out.view(*x.shape[:-1], self.weight.shape[0])
         out = w8a8_block_fp8_linear(x, self.weight, [128, 128], self.weight_scale, bias=self.bias)
         if self.reduce_results and self.tp_size > 1:
             out = tensor_model_parallel_all_reduce(out, self.group)
