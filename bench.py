@@ -291,15 +291,33 @@ def bench_parallel(S, device, rank: int, world: int, steps: int):
         flops += 2 * M * n * k
     del w
 
-    def tp_step():
+    from sglang_b200.peer_allreduce import PeerAllReduce
+
+    # row-parallel layers share one set of peer buffers per output width (N = 8192 for both)
+    peer = {}
+    for kind, x, wq, ws in layers:
+        if kind == "row" and wq.shape[0] not in peer:
+            peer[wq.shape[0]] = PeerAllReduce(M, wq.shape[0], torch.bfloat16)
+
+    def tp_step(rows: int, fused: bool):
         for kind, x, wq, ws in layers:
-            y = S.w8a8_block_fp8_linear(x, wq, [128, 128], ws)
+            if kind == "row" and fused:
+                peer[wq.shape[0]].linear_bf16_input(x[:rows], wq, ws)
+                continue
+            y = S.w8a8_block_fp8_linear(x[:rows], wq, [128, 128], ws)
             if kind == "row":
                 P.tensor_model_parallel_all_reduce(y)
 
-    ms = timed(tp_step, steps)
-    out["tp_llama70b_M4096"] = {"tflops": flops / ms / 1e9, "ms": ms, "tp": world,
-                                "allreduce_bytes_per_step": 2 * M * 8192 * 2}
+    # prefill-sized (M = 4096) and decode-sized (M = 16) steps, all-reduce by NCCL or fused with the
+    # GEMM over peer memory (fan-out epilogue + finishing kernel)
+    for rows in (M, 16):
+        for fused in (False, True):
+            ms = timed(lambda: tp_step(rows, fused), steps)
+            key = f"tp_llama70b_M{rows}" + ("_peer_fused" if fused else "")
+            out[key] = {"tflops": flops * rows / M / ms / 1e9, "ms": ms, "tp": world,
+                        "allreduce": "peer memory, fused with the GEMM" if fused else "nccl",
+                        "allreduce_bytes_per_step": 2 * rows * 8192 * 2}
+    del peer
     del layers
     torch.cuda.empty_cache()
 

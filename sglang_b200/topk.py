@@ -135,8 +135,8 @@ def grouped_topk(
     topk_group: Optional[int] = None,
     num_fused_shared_experts: int = 0,
     routed_scaling_factor: Optional[float] = None,
-    num_token_non_padded: Optional[torch.Tensor] = None,
     apply_routed_scaling_factor_on_output: bool = False,
+    num_token_non_padded: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Softmax scores, a group's score is its maximum (DeepSeek-V2 routing)."""
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
@@ -159,8 +159,8 @@ def biased_grouped_topk(
     topk_group: Optional[int] = None,
     num_fused_shared_experts: int = 0,
     routed_scaling_factor: Optional[float] = None,
-    num_token_non_padded: Optional[torch.Tensor] = None,
     apply_routed_scaling_factor_on_output: bool = False,
+    num_token_non_padded: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sigmoid scores; a group's score is the sum of its two best biased scores; keep
     ``topk_group`` groups; take the top-k biased scores among them; weights are the unbiased
@@ -207,12 +207,12 @@ def select_experts(
         if c.correction_bias is None:
             w, ids = grouped_topk(hidden_states, router_logits, c.top_k, c.renormalize, c.num_expert_group,
                                   c.topk_group, c.num_fused_shared_experts, c.routed_scaling_factor,
-                                  num_token_non_padded, c.apply_routed_scaling_factor_on_output)
+                                  c.apply_routed_scaling_factor_on_output, num_token_non_padded)
         else:
             w, ids = biased_grouped_topk(hidden_states, router_logits, c.correction_bias, c.top_k, c.renormalize,
                                          c.num_expert_group, c.topk_group, c.num_fused_shared_experts,
-                                         c.routed_scaling_factor, num_token_non_padded,
-                                         c.apply_routed_scaling_factor_on_output)
+                                         c.routed_scaling_factor, c.apply_routed_scaling_factor_on_output,
+                                         num_token_non_padded)
     else:
         w, ids = fused_topk(hidden_states, router_logits, c.top_k, c.renormalize, c.correction_bias, c.scoring_func,
                             num_token_non_padded)
