@@ -329,8 +329,9 @@ def bench_parallel(S, device, rank: int, world: int, steps: int):
     x = torch.randn(T, H, generator=g).bfloat16().to(device)
     logits = torch.randn(T, E, generator=g).to(device)
     tw, ti = biased_grouped_topk(x, logits, torch.zeros(E, device=device), topk, True, cfg["n_group"], cfg["topk_group"])
-    for mode, label in (("ep", "standard"), ("ep_a2a", "a2a")):
-        layer = P.FusedMoE(w1, w2, w1_s, w2_s, rank, world, mode=mode, presharded=True, num_experts=E)
+    for mode, label in (("ep", "standard"), ("ep_a2a", "a2a"), ("ep_peer", "a2a_peer_memory")):
+        layer = P.FusedMoE(w1, w2, w1_s, w2_s, rank, world, mode=mode, presharded=True, num_experts=E,
+                           max_tokens=T // world)
         if mode == "ep":
             xs, ws_, is_ = x, tw, ti
         else:

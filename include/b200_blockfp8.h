@@ -202,6 +202,36 @@ int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* o
                           void* const* residual_out, const void* rms_weight, float eps, void* my_flags,
                           void* const* peer_flags, uint32_t epoch, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Expert-parallel token exchange over peer memory (dispatch / combine around fused_experts)
+ * replaces: python/sglang/srt/layers/moe/token_dispatcher/deepep.py:507-602 (normal dispatch and
+ *           combine through DeepEP) and standard.py:172-210 (rebasing ids to the owning rank)
+ * Rank r owns experts [r*E/p, (r+1)*E/p). Every rank has a receive area indexed by source rank
+ * and source token position, four arrays of p*T_max positions: q [p][T_max][H] e4m3 bytes,
+ * s [p][T_max][H/128] fp32, w [p][T_max][topk] fp32, ids [p][T_max][topk] int32 (ids rebased to
+ * the owner, -1 = not for this rank or no token), and an output area out [p][T_max][H].
+ * recv_q/recv_s/recv_w/recv_ids/peer_out are HOST arrays with one device pointer per rank
+ * (that rank's area as mapped in this process; peer memory for other ranks).
+ * b200_ep_dispatch: for each local token t < T (global topk_ids [T,topk], -1 allowed) store
+ *   the row, scales, weights and rebased ids at position [rank][t] of every rank that owns one
+ *   of its experts, and ids = -1 at every other rank and for positions T <= t < T_max.
+ * b200_peer_handshake: epoch handshake with all ranks (flag arrays as for
+ *   b200_allreduce_finish; phase 0 or 1 selects the flag row; epoch strictly increasing per
+ *   phase). Bounded 2 s, then device status 2. After it returns (in stream order) everything the
+ *   other ranks stored before THEIR handshake of the same epoch is visible.
+ * (then: b200_fused_experts_fp8 over the p*T_max positions with hidden = q, hidden_scale = s,
+ *  out = this rank's output area)
+ * b200_ep_combine: out[t] = fp32 sum, in ascending owner rank, of peer_out[d][rank][t][:] over
+ *   the ranks d that own an expert of token t; out [T,H] bf16/f16. */
+int b200_ep_dispatch(const void* x_q, const float* x_s, const float* topk_weights,
+                     const int32_t* topk_ids, int64_t T, int64_t T_max, int topk, int64_t H, int E,
+                     int n_ranks, int rank, void* const* recv_q, void* const* recv_s,
+                     void* const* recv_w, void* const* recv_ids, void* stream);
+int b200_peer_handshake(void* my_flags, void* const* peer_flags, int n_ranks, int rank, int phase,
+                        uint32_t epoch, void* stream);
+int b200_ep_combine(void* const* peer_out, const int32_t* topk_ids, void* out, int dtype, int64_t T,
+                    int64_t T_max, int topk, int64_t H, int E, int n_ranks, int rank, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,16 @@ SIGNATURES = {
         [c_void_p, c_int64, POINTER(c_void_p), c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p,
          POINTER(c_void_p), c_void_p, c_float, c_void_p, POINTER(c_void_p), c_uint32, c_void_p],
     ),
+    "b200_ep_dispatch": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int, c_int, c_int,
+         POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), c_void_p],
+    ),
+    "b200_peer_handshake": (c_int, [c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_uint32, c_void_p]),
+    "b200_ep_combine": (
+        c_int,
+        [POINTER(c_void_p), c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int, c_int, c_int, c_void_p],
+    ),
     "b200_route_topk": (
         c_int,
         [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,

@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OUT_DIR = os.path.join(PKG, "_lib")
 LIB = os.path.join(OUT_DIR, "libb200_blockfp8.so")
-SOURCES = ["status.cu", "quant.cu", "align.cu", "gemm.cu", "moe.cu", "topk.cu", "comm.cu"]
+SOURCES = ["status.cu", "quant.cu", "align.cu", "gemm.cu", "moe.cu", "topk.cu", "comm.cu", "ep.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17",

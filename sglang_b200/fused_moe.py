@@ -63,8 +63,12 @@ def fused_experts_impl(
     routed_scaling_factor: Optional[float] = None,
     hidden_states_scale: Optional[torch.Tensor] = None,
     output_dtype: Optional[torch.dtype] = None,
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Checks of the reference's ``fused_experts_impl`` (fused_moe.py:824-834) + the launch.
+
+    ``out`` (extension): a preallocated contiguous result tensor, e.g. a region of peer-mapped
+    memory that other ranks read.
 
     ``hidden_states_scale`` (extension used by the expert-parallel all-to-all path): when given,
     ``hidden_states`` is already FP8 E4M3 ``[T, H]`` with row-major fp32 1x128 scales
@@ -100,7 +104,11 @@ def fused_experts_impl(
     topk_ids = topk_ids.to(torch.int32).contiguous()
     w1_scale = w1_scale.to(torch.float32).contiguous()
     w2_scale = w2_scale.to(torch.float32).contiguous()
-    if inplace:
+    if out is not None:
+        assert not inplace and out.is_contiguous() and out.dtype == out_dtype
+        assert tuple(out.shape) == ((T, topk, H) if no_combine else (T, H)), "preallocated output shape"
+        N.require_cuda(out)
+    elif inplace:
         out = hidden_states
     elif no_combine:
         out = torch.empty((T, topk, H), dtype=out_dtype, device=hidden_states.device)

@@ -229,16 +229,20 @@ class FusedMoE:
     """Block-FP8 MoE layer partitioned over a group.
 
     ``mode``: "tp" (split I, all-reduce), "ep" (standard: replicated tokens, local experts,
-    all-reduce), "ep_a2a" (tokens partitioned, all-to-all dispatch / combine). ``forward``
-    takes the tokens this rank holds (all tokens for "tp"/"ep", its partition for "ep_a2a")
-    and GLOBAL expert ids."""
+    all-reduce), "ep_a2a" (tokens partitioned, all-to-all dispatch / combine through
+    ``all_to_all_single``), "ep_peer" (tokens partitioned, dispatch / combine by this package's
+    kernels over NVLink peer memory, ``peer_ep.PeerExpertParallel``; ``max_tokens`` local tokens
+    at most). ``forward`` takes the tokens this rank holds (all tokens for "tp"/"ep", its
+    partition otherwise) and GLOBAL expert ids."""
 
     def __init__(self, w1, w2, w1_s, w2_s, rank: int, size: int, mode: str = "ep", group=None,
-                 expert_fn: Optional[Callable] = None, presharded: bool = False, num_experts: Optional[int] = None):
+                 expert_fn: Optional[Callable] = None, presharded: bool = False, num_experts: Optional[int] = None,
+                 max_tokens: int = 8192):
         """``presharded``: the four tensors are already this rank's shard (a loader that never
         materialises the full layer); ``num_experts`` then gives the global expert count."""
-        assert mode in ("tp", "ep", "ep_a2a")
+        assert mode in ("tp", "ep", "ep_a2a", "ep_peer")
         self.mode, self.rank, self.size, self.group = mode, rank, size, group
+        self.max_tokens, self._peer = max_tokens, None
         if presharded:
             self.num_experts = num_experts if num_experts is not None else w1.shape[0] * (1 if mode == "tp" else size)
             self.w1, self.w2, self.w1_s, self.w2_s = w1, w2, w1_s, w2_s
@@ -265,6 +269,19 @@ class FusedMoE:
             ids = local_expert_ids(topk_ids, self.num_experts, self.size, self.rank)
             out = self._experts(hidden_states, None, topk_weights, ids, hidden_states.dtype)
             return tensor_model_parallel_all_reduce(out, self.group) if self.size > 1 else out
+        if self.mode == "ep_peer":
+            from .fused_moe import fused_experts_impl
+            from .peer_ep import PeerExpertParallel
+
+            if self._peer is None:
+                self._peer = PeerExpertParallel(self.max_tokens, hidden_states.shape[1], topk_ids.shape[1],
+                                                self.num_experts, hidden_states.dtype, self.group)
+
+            def experts(q, s, w, ids, out):
+                fused_experts_impl(q, self.w1, self.w2, w, ids, self.w1_s, self.w2_s, inplace=False,
+                                   hidden_states_scale=s, output_dtype=out.dtype, out=out)
+
+            return self._peer.forward(hidden_states, topk_weights, topk_ids, experts)
         from .fp8_kernel import per_token_group_quant_fp8
 
         quant = getattr(self, "_quant_fn", None) or (lambda t: per_token_group_quant_fp8(t, 128))

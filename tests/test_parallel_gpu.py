@@ -57,6 +57,13 @@ def _worker(rank, world, port, results):
         sl = slice(rank * per, (rank + 1) * per)
         out = P.FusedMoE(*dev, rank, world, mode="ep_a2a")(xm[sl].cuda(), tw[sl].cuda(), ti[sl].cuda())
         res["ep_a2a"] = O.rel_frobenius(out.float().cpu(), ref[sl])
+        # dispatch / combine by the package's own kernels over peer memory; several calls with
+        # different token counts reuse the same areas
+        peer = P.FusedMoE(*dev, rank, world, mode="ep_peer", max_tokens=per + 3)
+        for rep, cnt in enumerate([per, per - 5, per]):
+            sl = slice(rank * per, rank * per + cnt)
+            out = peer(xm[sl].cuda(), tw[sl].cuda(), ti[sl].cuda())
+            res[f"ep_peer_{rep}"] = O.rel_frobenius(out.float().cpu(), ref[sl])
         res["status"] = _native.read_device_status()
         results[rank] = res
     finally:
