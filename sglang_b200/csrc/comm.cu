@@ -9,7 +9,7 @@
 //   3. two-shot only: the owner of a 128-row block writes its result into every rank's output.
 // Handshakes are epoch counters in a small flag array per rank: rank r writes epoch into
 // peer[d].flags[r] with a system-scope release after a system fence, and polls its own
-// flags[0..n) with system-scope acquires. Every poll is bounded (2 s): on expiry the kernel
+// flags[0..n) with system-scope acquires. Every poll is bounded (2 s by default): on expiry the kernel
 // records status 2 in the device status word and returns without touching peer memory again.
 // Slots written by peers are read with L2-only loads (ld.global.cg): the L1 of this SM may
 // still hold lines of the previous call that used the same buffer.
@@ -18,7 +18,6 @@
 namespace b200 {
 
 constexpr int kMaxRanks = 8;
-constexpr unsigned long long kWaitNs = 2000000000ull;
 
 struct AllReduceParams {
   const void* slots;  // local [n_ranks][slot_stride], slot r = rank r's partial [M][N]
@@ -35,6 +34,7 @@ struct AllReduceParams {
   int by_tile;  // two-shot: reduce only row blocks mt % n_ranks == rank, write them to every rank
   uint32_t epoch;
   float eps;
+  unsigned long long wait_ns;  // limit of every poll
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -55,7 +55,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // `phase` selects the flag row. Epochs only grow, so `>=` tolerates a rank that is already a
 // call ahead.
 __device__ bool handshake(uint32_t* my_flags, uint32_t* const* peer_flags, int n, int rank, int phase, uint32_t epoch,
-                          bool signal) {
+                          bool signal, unsigned long long wait_ns) {
   const int d = threadIdx.x;
   bool ok = true;
   if (d < n) {
@@ -65,7 +65,7 @@ __device__ bool handshake(uint32_t* my_flags, uint32_t* const* peer_flags, int n
     }
     const unsigned long long t0 = now_ns();
     while ((int32_t)(ld_acquire_sys(my_flags + phase * kMaxRanks + d) - epoch) < 0) {
-      if (now_ns() - t0 > kWaitNs) {
+      if (now_ns() - t0 > wait_ns) {
         ok = false;
         break;
       }
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   // block 0 announces this rank's partials; every block waits for all ranks' announcements
-  if (!handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 0, p.epoch, blockIdx.x == 0)) atomicExch(&s_ok, 0);
+  if (!handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 0, p.epoch, blockIdx.x == 0, p.wait_ns)) atomicExch(&s_ok, 0);
   __syncthreads();
   if (!s_ok) {
     if (threadIdx.x == 0) atomicCAS(p.status, 0, 2);
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
 
 // Two-shot tail: "my results are in your output" handshake (flag row 1). One block.
 __global__ void __launch_bounds__(32) allreduce_results_landed_kernel(const AllReduceParams p) {
-  const bool ok = handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 1, p.epoch, true);
+  const bool ok = handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 1, p.epoch, true, p.wait_ns);
   if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) atomicCAS(p.status, 0, 2);
 }
 
@@ -190,7 +190,7 @@ extern "C" int b200_allreduce_finish(const void* slots, int64_t slot_stride, voi
   AllReduceParams p = {};
   p.slots = slots; p.slot_stride = slot_stride; p.residual = residual; p.rms_weight = rms_weight;
   p.my_flags = static_cast<uint32_t*>(my_flags); p.M = M; p.N = N; p.n_ranks = n_ranks; p.rank = rank;
-  p.by_tile = by_tile != 0; p.epoch = epoch; p.eps = eps;
+  p.by_tile = by_tile != 0; p.epoch = epoch; p.eps = eps; p.wait_ns = peer_wait_ns();
   p.status = device_status_word();
   if (!p.status) {
     set_error_detail("cannot resolve the device status word");

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/b200_blockfp8.h"
 
@@ -42,6 +43,17 @@ inline int check_launch(const char* what) {
     return B200_E_LAUNCH;
   }
   return B200_OK;
+}
+
+// Limit of a device-side wait for another GPU (handshakes of the peer-memory collectives), in
+// nanoseconds: 2 s unless B200_PEER_WAIT_MS says otherwise (clamped to 100 ms .. 60 s). Ranks
+// that can drift further apart than this on the host must synchronise on the host first.
+inline unsigned long long peer_wait_ns() {
+  long ms = 2000;
+  if (const char* e = getenv("B200_PEER_WAIT_MS")) ms = atol(e);
+  if (ms < 100) ms = 100;
+  if (ms > 60000) ms = 60000;
+  return (unsigned long long)ms * 1000000ull;
 }
 
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -114,13 +114,15 @@ __global__ void __launch_bounds__(128) ep_combine_kernel(const EpCombineParams a
 
 // Epoch handshake: thread d signals rank d (system fence, release store of `epoch` into
 // peer[d].flags[phase][rank]) and waits until its own flags[phase][d] has reached `epoch`.
-// Bounded: after 2 s the device status word becomes 2 and the kernel returns.
+// Bounded: after the wait limit (2 s by default) the device status word becomes 2 and the kernel
+// returns.
 struct HandshakeParams {
   uint32_t* my_flags;
   uint32_t* peer_flags[kEpMaxRanks];
   int* status;
   int p, rank, phase;
   uint32_t epoch;
+  unsigned long long wait_ns;
 };
 
 __global__ void __launch_bounds__(32) peer_handshake_kernel(const HandshakeParams a) {
@@ -137,7 +139,7 @@ __global__ void __launch_bounds__(32) peer_handshake_kernel(const HandshakeParam
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flags + a.phase * kEpMaxRanks + d) : "memory");
       if ((int32_t)(v - a.epoch) >= 0) break;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-      if (t1 - t0 > 2000000000ull) {
+      if (t1 - t0 > a.wait_ns) {
         ok = false;
         break;
       }
@@ -205,6 +207,7 @@ extern "C" int b200_peer_handshake(void* my_flags, void* const* peer_flags, int 
                  "peer_handshake: bad arguments (ranks=%d rank=%d phase=%d)", n_ranks, rank, phase);
   HandshakeParams a = {};
   a.my_flags = static_cast<uint32_t*>(my_flags); a.p = n_ranks; a.rank = rank; a.phase = phase; a.epoch = epoch;
+  a.wait_ns = peer_wait_ns();
   a.status = device_status_word();
   if (!a.status) {
     set_error_detail("cannot resolve the device status word");

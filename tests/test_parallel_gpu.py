@@ -40,7 +40,7 @@ def _worker(rank, world, port, results):
         res["col_gather"] = O.rel_frobenius(colg(x.cuda()).float().cpu(), h_ref.float())
 
         # ---- MoE: TP over I, standard EP, all-to-all EP
-        T, E, topk, H, I = 64, 8, 2, 512, 256
+        T, E, topk, H, I = 64, 8, 2, 512, 512
         g = torch.Generator().manual_seed(7)
         xm = torch.randn(T, H, generator=g).bfloat16()
         w1 = torch.stack([make_weight(2 * I, H, 10 + e)[0] for e in range(E)])
@@ -60,9 +60,12 @@ def _worker(rank, world, port, results):
         # dispatch / combine by the package's own kernels over peer memory; several calls with
         # different token counts reuse the same areas
         peer = P.FusedMoE(*dev, rank, world, mode="ep_peer", max_tokens=per + 3)
+        outs = []
+        dist.barrier()  # ranks enter the handshakes together (their wait limit is 2 s)
         for rep, cnt in enumerate([per, per - 5, per]):
             sl = slice(rank * per, rank * per + cnt)
-            out = peer(xm[sl].cuda(), tw[sl].cuda(), ti[sl].cuda())
+            outs.append((sl, peer(xm[sl].cuda(), tw[sl].cuda(), ti[sl].cuda()).clone()))
+        for rep, (sl, out) in enumerate(outs):
             res[f"ep_peer_{rep}"] = O.rel_frobenius(out.float().cpu(), ref[sl])
         res["status"] = _native.read_device_status()
         results[rank] = res
@@ -70,14 +73,16 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp_and_ep_two_ranks():
-    port = 33500 + os.getpid() % 2000
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_and_ep_ranks(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = 33500 + os.getpid() % 2000 + world
     with mp.Manager() as m:
         results = m.dict()
-        mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+        mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
         results = dict(results)
-    assert set(results) == {0, 1}
+    assert set(results) == set(range(world))
     for r, res in results.items():
         assert res.pop("status") == 0
         for k, v in res.items():

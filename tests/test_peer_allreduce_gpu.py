@@ -126,32 +126,42 @@ def _worker(rank, world, port, results):
         resid = torch.randn(512, Nn, generator=g).bfloat16()
         gamma = (torch.rand(Nn, generator=g) + 0.5).bfloat16()
         nccl = P.RowParallelLinear(wq.cuda(), ws.cuda(), rank, world)
+        # All CPU-side oracle work first: ranks must not drift apart by more than the kernels'
+        # wait limit (2 s) between the launches of one collective call.
+        cases = []
+        for rep, M in enumerate([16, 300, 512, 1, 300, 130]):  # several calls: buffer parity and epochs
+            x = make_activation(M, K, 10 + rep)
+            ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
+            acc = ref + resid[:M].float()
+            normed = acc * torch.rsqrt(acc.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+            cases.append((M, x[:, rank * kl : (rank + 1) * kl].contiguous().cuda(), ref, acc, normed))
+        x = make_activation(96, K, 99)
+        layer_x = x[:, rank * kl : (rank + 1) * kl].contiguous().cuda()
+        layer_ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
+        got = {}
         for two_shot in (False, True):
             par = PeerAllReduce(512, Nn, torch.bfloat16, two_shot=two_shot)
             tag = "two" if two_shot else "one"
-            for rep, M in enumerate([16, 300, 512, 1, 300, 130]):  # several calls: buffer parity and epochs
-                x = make_activation(M, K, 10 + rep)
-                xl = x[:, rank * kl : (rank + 1) * kl].contiguous().cuda()
-                ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
+            dist.barrier()
+            for rep, (M, xl, ref, acc, normed) in enumerate(cases):
                 out, _ = par.linear_bf16_input(xl, wl, wsl)
-                res[f"{tag}_{rep}_sum"] = O.rel_frobenius(out.float().cpu(), ref)
-                res[f"{tag}_{rep}_vs_nccl"] = O.rel_frobenius(out.float().cpu(), nccl(xl).float().cpu())
-                # every rank must hold the same bits
+                got[f"{tag}_{rep}_sum"] = (out.clone(), ref)
+                got[f"{tag}_{rep}_vs_nccl"] = (out.clone(), nccl(xl).float().cpu())
                 both = [torch.empty_like(out) for _ in range(world)]
                 dist.all_gather(both, out.contiguous())
+                # every rank must hold the same bits
                 res[f"{tag}_{rep}_same_bits"] = 0.0 if all(torch.equal(both[0], b) for b in both) else 1.0
                 r = resid[:M].contiguous().cuda()
                 out, r_out = par.linear_bf16_input(xl, wl, wsl, residual=r, rms_weight=gamma.cuda(), eps=1e-6)
-                acc = ref + resid[:M].float()
-                res[f"{tag}_{rep}_resid"] = O.rel_frobenius(r_out.float().cpu(), acc)
-                normed = acc * torch.rsqrt(acc.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
-                res[f"{tag}_{rep}_norm"] = O.rel_frobenius(out.float().cpu(), normed)
+                got[f"{tag}_{rep}_resid"] = (r_out.clone(), acc)
+                got[f"{tag}_{rep}_norm"] = (out.clone(), normed)
         # through the layer object
-        x = make_activation(96, K, 99)
-        xl = x[:, rank * kl : (rank + 1) * kl].contiguous().cuda()
         row = P.RowParallelLinear(wq.cuda(), ws.cuda(), rank, world, reduce_mode="peer", max_tokens=128)
-        ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
-        res["layer"] = O.rel_frobenius(row(xl).float().cpu(), ref)
+        dist.barrier()
+        got["layer"] = (row(layer_x).clone(), layer_ref)
+        torch.cuda.synchronize()
+        for key, (mine, ref) in got.items():
+            res[key] = O.rel_frobenius(mine.float().cpu(), ref)
         torch.cuda.synchronize()
         res["status"] = _native.read_device_status()
         results[rank] = res
@@ -159,14 +169,16 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_peer_allreduce_two_ranks():
-    port = 35500 + os.getpid() % 2000
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_allreduce_ranks(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = 35500 + os.getpid() % 2000 + world
     with mp.Manager() as m:
         results = m.dict()
-        mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+        mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
         results = dict(results)
-    assert set(results) == {0, 1}
+    assert set(results) == set(range(world))
     for r, res in results.items():
         assert res.pop("status") == 0
         for k, v in res.items():
