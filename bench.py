@@ -318,6 +318,28 @@ def bench_parallel(S, device, rank: int, world: int, steps: int):
                         "allreduce": "peer memory, fused with the GEMM" if fused else "nccl",
                         "allreduce_bytes_per_step": 2 * rows * 8192 * 2}
     del peer
+    # the decode-sized step again, replayed from a CUDA graph (how a server runs decode): the peer
+    # path uses device-side epochs and a single slot buffer so that the capture can be replayed
+    peer = {n_: PeerAllReduce(16, n_, torch.bfloat16, graph_safe=True)
+            for n_ in {wq.shape[0] for kind, _, wq, _ in layers if kind == "row"}}
+    for fused in (False, True):
+        key = "tp_llama70b_M16_graph" + ("_peer_fused" if fused else "")
+        try:
+            stream = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                tp_step(16, fused)
+                torch.cuda.synchronize()
+                barrier(world)
+                with torch.cuda.graph(graph, stream=stream):
+                    tp_step(16, fused)
+            ms = timed(graph.replay, steps)
+            out[key] = {"ms": ms, "tp": world, "allreduce": "peer memory, fused with the GEMM" if fused else "nccl"}
+        except Exception as e:  # a capture that fails must not take the other line items with it
+            out[key] = {"error": repr(e)}
+            torch.cuda.synchronize()
+            barrier(world)
+    del peer
     del layers
     torch.cuda.empty_cache()
 

@@ -189,7 +189,10 @@ int b200_route_topk(const void* logits, int logits_dtype, const float* correctio
  * reduced and the results are written to out[0..n_ranks) and residual_out[0..n_ranks) (every
  * rank's buffers; `out` and `residual_out` are HOST arrays of device pointers, NULL = none), followed
  * by a second handshake so that on return (in stream order) every rank's output is complete.
- * All waits are bounded (2 s); on expiry the device status word becomes 2. */
+ * epoch == 0 selects device-side epochs (a counter next to the flags, flags[16..18], advanced by
+ * the kernels themselves): the identical call can then be replayed from a CUDA graph; a flag array
+ * is driven either by host epochs or by device epochs, never both. The flag array is 32 uint32.
+ * All waits are bounded (2 s, B200_PEER_WAIT_MS); on expiry the device status word becomes 2. */
 size_t b200_w8a8_block_fp8_gemm_fanout_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int b200_w8a8_block_fp8_gemm_fanout(const void* A, const float* As, int64_t as_stride_m,
                                     int64_t as_stride_k, const void* B, const float* Bs,
@@ -217,7 +220,7 @@ int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* o
  *   of its experts, and ids = -1 at every other rank and for positions T <= t < T_max.
  * b200_peer_handshake: epoch handshake with all ranks (flag arrays as for
  *   b200_allreduce_finish; phase 0 or 1 selects the flag row; epoch strictly increasing per
- *   phase). Bounded 2 s, then device status 2. After it returns (in stream order) everything the
+ *   phase, or 0 for device-side epochs as above). Bounded 2 s, then device status 2. After it returns (in stream order) everything the
  *   other ranks stored before THEIR handshake of the same epoch is visible.
  * (then: b200_fused_experts_fp8 over the p*T_max positions with hidden = q, hidden_scale = s,
  *  out = this rank's output area)

@@ -11,6 +11,10 @@
 // peer[d].flags[r] with a system-scope release after a system fence, and polls its own
 // flags[0..n) with system-scope acquires. Every poll is bounded (2 s by default): on expiry the kernel
 // records status 2 in the device status word and returns without touching peer memory again.
+// epoch == 0 selects device-side epochs: the call's epoch is 1 + a counter kept next to the flags
+// (flags[16 + phase]), bumped by the last block of the kernel, so the identical launch can be
+// replayed from a CUDA graph; all ranks then advance in lockstep because they replay the same
+// sequence of calls. A flag array is used with host epochs or with device epochs, never both.
 // Slots written by peers are read with L2-only loads (ld.global.cg): the L1 of this SM may
 // still hold lines of the previous call that used the same buffer.
 #include "common.cuh"
@@ -75,17 +79,38 @@ __device__ bool handshake(uint32_t* my_flags, uint32_t* const* peer_flags, int n
   return ok;
 }
 
+constexpr int kCounterBase = 2 * kMaxRanks;  // flags[16 + phase]: device-side epoch counters
+constexpr int kTicket = kCounterBase + 2;     // flags[18]: blocks of the running kernel that are done
+
+// Last block out bumps the device-side epoch counter of `phase` (device epochs only).
+__device__ void finish_epoch(uint32_t* my_flags, int phase, bool device_epoch) {
+  if (!device_epoch) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(my_flags + kTicket, 1u) == gridDim.x - 1) {
+      my_flags[kTicket] = 0;
+      __threadfence();
+      atomicAdd(my_flags + kCounterBase + phase, 1u);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReduceParams p) {
   __shared__ int s_ok;
   __shared__ float s_red[8];
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
+  const bool device_epoch = p.epoch == 0;
+  // stable for the whole kernel: the counter moves only when every block has finished
+  const uint32_t epoch = device_epoch ? *reinterpret_cast<volatile uint32_t*>(p.my_flags + kCounterBase) + 1u : p.epoch;
   // block 0 announces this rank's partials; every block waits for all ranks' announcements
-  if (!handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 0, p.epoch, blockIdx.x == 0, p.wait_ns)) atomicExch(&s_ok, 0);
+  if (!handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 0, epoch, blockIdx.x == 0, p.wait_ns)) atomicExch(&s_ok, 0);
   __syncthreads();
   if (!s_ok) {
     if (threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+    finish_epoch(p.my_flags, 0, device_epoch);
     return;
   }
   const int64_t N = p.N;
@@ -159,12 +184,16 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
       }
     }
   }
+  finish_epoch(p.my_flags, 0, device_epoch);
 }
 
 // Two-shot tail: "my results are in your output" handshake (flag row 1). One block.
 __global__ void __launch_bounds__(32) allreduce_results_landed_kernel(const AllReduceParams p) {
-  const bool ok = handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 1, p.epoch, true, p.wait_ns);
+  const bool device_epoch = p.epoch == 0;
+  const uint32_t epoch = device_epoch ? *reinterpret_cast<volatile uint32_t*>(p.my_flags + kCounterBase + 1) + 1u : p.epoch;
+  const bool ok = handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 1, epoch, true, p.wait_ns);
   if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+  finish_epoch(p.my_flags, 1, device_epoch);
 }
 
 }  // namespace b200

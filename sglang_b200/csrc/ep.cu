@@ -128,16 +128,21 @@ struct HandshakeParams {
 __global__ void __launch_bounds__(32) peer_handshake_kernel(const HandshakeParams a) {
   const int d = threadIdx.x;
   bool ok = true;
+  // epoch 0 = device-side epochs: 1 + the counter kept at flags[16 + phase] (bumped below), so the
+  // identical launch can be replayed from a CUDA graph
+  uint32_t* counter = a.my_flags + 2 * kEpMaxRanks + a.phase;
+  const uint32_t epoch = a.epoch != 0 ? a.epoch : *reinterpret_cast<volatile uint32_t*>(counter) + 1u;
+  __syncwarp();
   if (d < a.p) {
     __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[d] + a.phase * kEpMaxRanks + a.rank), "r"(a.epoch)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[d] + a.phase * kEpMaxRanks + a.rank), "r"(epoch)
                  : "memory");
     unsigned long long t0, t1;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
     for (;;) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flags + a.phase * kEpMaxRanks + d) : "memory");
-      if ((int32_t)(v - a.epoch) >= 0) break;
+      if ((int32_t)(v - epoch) >= 0) break;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
       if (t1 - t0 > a.wait_ns) {
         ok = false;
@@ -147,6 +152,7 @@ __global__ void __launch_bounds__(32) peer_handshake_kernel(const HandshakeParam
     }
   }
   if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) atomicCAS(a.status, 0, 2);
+  if (a.epoch == 0 && threadIdx.x == 0) *counter = epoch;
 }
 
 }  // namespace b200

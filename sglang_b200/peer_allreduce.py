@@ -41,7 +41,10 @@ class PeerAllReduce:
     rows and exactly ``n`` columns, dtype bf16 or fp16."""
 
     def __init__(self, max_tokens: int, n: int, dtype: torch.dtype = torch.bfloat16, group=None,
-                 two_shot: Optional[bool] = None):
+                 two_shot: Optional[bool] = None, graph_safe: bool = False):
+        """``graph_safe``: calls can be captured in a CUDA graph and replayed. Epochs then live on
+        the device (advanced by the kernels), one slot buffer is used instead of two, and the
+        one-shot mode ends with a second handshake ("I have read my slots") that orders the reuse."""
         import torch.distributed._symmetric_memory as symm
 
         assert dist.is_initialized(), "torch.distributed must be initialised (one process per GPU, NCCL)"
@@ -51,6 +54,7 @@ class PeerAllReduce:
         assert self.world <= MAX_RANKS
         self.max_tokens, self.n, self.dtype = max_tokens, n, dtype
         self.two_shot = (self.world > 2) if two_shot is None else two_shot
+        self.graph_safe = graph_safe
         dev = torch.device("cuda", torch.cuda.current_device())
         self.device = dev
         esz = 2
@@ -94,7 +98,8 @@ class PeerAllReduce:
         assert weight.shape[1] == k and x_q.is_contiguous() and weight.is_contiguous()
         lib = N.load()
         self.epoch += 1
-        parity = self.epoch & 1
+        parity = 0 if self.graph_safe else self.epoch & 1
+        epoch_arg = 0 if self.graph_safe else self.epoch & 0xFFFFFFFF
         code = N.DTYPE_CODE[self.dtype]
         dests = (ctypes.c_void_p * self.world)(*[self._slot_ptr(d, parity, self.rank) for d in range(self.world)])
         ws_bytes = lib.b200_w8a8_block_fp8_gemm_fanout_workspace_bytes(m, n, k)
@@ -131,9 +136,13 @@ class PeerAllReduce:
             st = lib.b200_allreduce_finish(
                 self._slot_ptr(self.rank, parity, 0), self.slot_elems, outs, code, m, n, self.world, self.rank, int(self.two_shot),
                 N.ptr(residual), res_outs, N.ptr(rms_weight), float(eps), self.base[self.rank] + self.off_flags,
-                self._peer_flags, self.epoch & 0xFFFFFFFF, stream,
+                self._peer_flags, epoch_arg, stream,
             )
             N.check(st, "allreduce_finish")
+            if self.graph_safe and not self.two_shot:
+                st = lib.b200_peer_handshake(self.base[self.rank] + self.off_flags, self._peer_flags, self.world,
+                                             self.rank, 1, 0, stream)
+                N.check(st, "peer_handshake")
         return out, res_out
 
     def linear_bf16_input(self, x: torch.Tensor, weight, weight_scale, **kw):

@@ -32,7 +32,9 @@ from .fp8_kernel import fp8_dtype, per_token_group_quant_fp8
 
 class PeerExpertParallel:
     def __init__(self, max_tokens: int, hidden: int, topk: int, num_experts: int,
-                 dtype: torch.dtype = torch.bfloat16, group=None):
+                 dtype: torch.dtype = torch.bfloat16, group=None, graph_safe: bool = False):
+        """``graph_safe``: epochs live on the device (advanced by the handshake kernels), so a
+        captured ``forward`` can be replayed from a CUDA graph."""
         import torch.distributed._symmetric_memory as symm
 
         assert dist.is_initialized(), "torch.distributed must be initialised (one process per GPU, NCCL)"
@@ -63,6 +65,7 @@ class PeerExpertParallel:
         torch.cuda.synchronize(dev)
         dist.barrier(self.group)
         self.epoch = 0
+        self.graph_safe = graph_safe
         arr = ctypes.c_void_p * self.world
         self._recv_q = arr(*[b + self.off_q for b in self.base])
         self._recv_s = arr(*[b + self.off_s for b in self.base])
@@ -80,7 +83,7 @@ class PeerExpertParallel:
 
     def _handshake(self, phase: int, stream: int) -> None:
         st = N.load().b200_peer_handshake(self.base[self.rank] + self.off_flags, self._peer_flags, self.world, self.rank,
-                                          phase, self.epoch & 0xFFFFFFFF, stream)
+                                          phase, 0 if self.graph_safe else self.epoch & 0xFFFFFFFF, stream)
         N.check(st, "peer_handshake")
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,

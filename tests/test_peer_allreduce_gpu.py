@@ -107,6 +107,42 @@ def test_finish_kernel_single_rank_sum_residual_rmsnorm(M, N, mode):
         assert torch.equal(out, acc.bfloat16())
 
 
+def test_device_epochs_replay_from_a_cuda_graph_single_rank():
+    """epoch = 0: the kernels keep the epoch on the device, so the captured launch replays."""
+    from sglang_b200 import _native as N_
+
+    lib = N_.load()
+    M, N = 64, 512
+    slot = torch.randn(M, N, device="cuda").bfloat16()
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    outs = (ctypes.c_void_p * 1)(out.data_ptr())
+    peers = (ctypes.c_void_p * 1)(flags.data_ptr())
+    s = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        def call():
+            st = lib.b200_allreduce_finish(slot.data_ptr(), M * N, outs, N_.BF16, M, N, 1, 0, 0, None, None, None, 1e-6,
+                                           flags.data_ptr(), peers, 0, N_.current_stream())
+            N_.check(st, "finish")
+            N_.check(lib.b200_peer_handshake(flags.data_ptr(), peers, 1, 0, 1, 0, N_.current_stream()), "handshake")
+        call()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            call()
+            call()
+    for i in range(3):
+        slot.copy_(torch.randn(M, N, device="cuda").bfloat16())
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, slot)
+    assert N_.read_device_status() == 0
+    # 1 eager + 3 replays of 2 calls = 7 epochs on both phases; the block ticket is back at zero
+    assert flags[16].item() == 7 and flags[17].item() == 7 and flags[18].item() == 0
+    assert flags[0].item() == 7 and flags[8].item() == 7
+
+
 def _worker(rank, world, port, results):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -155,6 +191,39 @@ def _worker(rank, world, port, results):
                 out, r_out = par.linear_bf16_input(xl, wl, wsl, residual=r, rms_weight=gamma.cuda(), eps=1e-6)
                 got[f"{tag}_{rep}_resid"] = (r_out.clone(), acc)
                 got[f"{tag}_{rep}_norm"] = (out.clone(), normed)
+        # captured in a CUDA graph (device-side epochs, single slot buffer): two calls per graph,
+        # replayed with new inputs
+        import sglang_b200 as S
+
+        M, xl, ref, acc, normed = cases[1]
+        for two_shot in (False, True):
+            par = PeerAllReduce(512, Nn, torch.bfloat16, two_shot=two_shot, graph_safe=True)
+            xq, xs = S.per_token_group_quant_fp8(xl, 128, column_major_scales=True)
+            xq_static, xs_static = xq.clone(), xs.clone()
+            stream = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            dist.barrier()
+            with torch.cuda.stream(stream):
+                par.linear(xq_static, xs_static, wl, wsl)  # warm-up (workspace, module load)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=stream):
+                    o1, _ = par.linear(xq_static, xs_static, wl, wsl)
+                    o1 = o1.clone()
+                    o2, _ = par.linear(xq_static, xs_static, wl, wsl)
+                    o2 = o2.clone()
+            for rep in (1, 2, 4):
+                M2, xl2, ref2, _, _ = cases[rep]
+                if M2 != M:
+                    continue
+                q2, s2 = S.per_token_group_quant_fp8(xl2, 128, column_major_scales=True)
+                xq_static.copy_(q2)
+                xs_static.copy_(s2)
+                dist.barrier()
+                graph.replay()
+                torch.cuda.synchronize()
+                tag = "two" if two_shot else "one"
+                got[f"graph_{tag}_{rep}_a"] = (o1.clone(), ref2)
+                got[f"graph_{tag}_{rep}_b"] = (o2.clone(), ref2)
         # through the layer object
         row = P.RowParallelLinear(wq.cuda(), ws.cuda(), rank, world, reduce_mode="peer", max_tokens=128)
         dist.barrier()
