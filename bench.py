@@ -437,25 +437,59 @@ def main():
     h2d = sum(x.numel() * x.element_size() for x in acts_host.values())
     d2h = sum(x.numel() * x.element_size() for x in outs_host.values())
 
+    # The copies run on their own streams so that the H2D copy of one linear, the kernels of the
+    # previous one and the D2H copy of the one before overlap (both PCIe directions busy at once);
+    # every byte still crosses inside the timed region. Device input buffers are double-buffered
+    # per linear; an event per buffer says when the kernels have finished reading it.
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_in = {name: [torch.empty_like(acts_dev[name]) for _ in range(2)] for name, _, _ in LINEARS}
+    consumed = {name: [None, None] for name, _, _ in LINEARS}
+    step_no = [0]
+
     def e2e_step():
-        dev = {name: acts_host[name].to(device, non_blocking=True) for name, _, _ in LINEARS}
-        outs = run_step(S, dev, weights)
-        for name, _, _ in LINEARS:
-            outs_host[name].copy_(outs[name], non_blocking=True)
+        b = step_no[0] & 1
+        step_no[0] += 1
+        last = None
+        for name, n, k in LINEARS:
+            wq, ws = weights[name]
+            buf = dev_in[name][b]
+            with torch.cuda.stream(s_in):
+                if consumed[name][b] is not None:
+                    s_in.wait_event(consumed[name][b])
+                buf.copy_(acts_host[name], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            main.wait_event(arrived)
+            q, sc = S.per_token_group_quant_fp8(buf, 128, column_major_scales=True)
+            out = S.w8a8_block_fp8_matmul(q, wq, sc, ws, [128, 128], torch.bfloat16)
+            done = torch.cuda.Event()
+            done.record(main)
+            consumed[name][b] = done
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                outs_host[name].copy_(out, non_blocking=True)
+                out.record_stream(s_out)
+                last = torch.cuda.Event()
+                last.record(s_out)
+        return last
 
     for _ in range(2):
         e2e_step()
+    torch.cuda.synchronize()
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = max(3, min(args.steps, 10))
     e0.record()
     for _ in range(e2e_steps):
-        e2e_step()
+        last = e2e_step()
+    main.wait_event(last)  # the timed region ends when the last result is in host memory
     e1.record()
     barrier(world)
     e2e_ms = dist_max(e0.elapsed_time(e1) / e2e_steps, world, device)
     e2e = {"value": world * M_ROWS * FLOPS_PER_ROW / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps}
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "overlap": "H2D, kernels and D2H of consecutive linears run on three streams; every copy is inside the timed region"}
 
     line = {
         "metric": "block-FP8 GEMM TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
