@@ -145,6 +145,24 @@ int b200_fused_experts_fp8(const void* hidden, const float* hidden_scale, int h_
                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Experts over the masked (low-latency) layout: tokens already grouped by expert
+ * replaces: python/sglang/srt/layers/moe/moe_runner/deep_gemm.py:362-494 (_run_masked_gemm:
+ *           masked grouped GEMM -> SiLU*mul + 1x128 re-quant -> masked grouped GEMM) and the
+ *           activation kernel python/sglang/srt/layers/moe/ep_moe/kernels.py:288-431
+ * hidden_q [E,T_pad,H] e4m3 with row-major fp32 scales hidden_s [E,T_pad,H/128]; only the first
+ * masked_m[e] rows of expert e are valid (int32 [E] on the device, clamped to [0,T_pad]).
+ * w1 [E,2I,H] (gate rows then up rows), w2 [E,H,I] e4m3 with fp32 128x128 block scales as for
+ * b200_fused_experts_fp8. out [E,T_pad,H] bf16/f16: rows t < masked_m[e] are written, the others
+ * are left untouched. No router weights (the combine step of the caller applies them).
+ * T_pad % 128 == 0, H % 128 == 0, I % 128 == 0. */
+size_t b200_masked_experts_fp8_workspace_bytes(int E, int64_t T_pad, int64_t H, int64_t I);
+int b200_masked_experts_fp8(const void* hidden_q, const float* hidden_s, const void* w1,
+                            const void* w2, const float* w1_scale, const float* w2_scale,
+                            const int32_t* masked_m, void* out, int out_dtype, int E, int64_t T_pad,
+                            int64_t H, int64_t I, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Expert routing (the step before fused_experts): scores -> top-k weights and expert ids
  * replaces: python/sglang/srt/layers/moe/topk.py:550-588 (fused_topk_torch_native) and :640-700
  *           (fused_topk -> sgl-kernel topk_softmax / topk_sigmoid,

@@ -53,6 +53,7 @@ __all__ = [
     "moe_align_block_size",
     "silu_and_mul",
     "fused_experts_fp8",
+    "masked_experts_fp8",
     "softmax_topk",
     "biased_grouped_topk",
     "sigmoid_topk",
@@ -271,6 +272,23 @@ def fused_experts_fp8(
     out = out.sum(dim=1)
     if routed_scaling_factor is not None:
         out = out * routed_scaling_factor
+    return out
+
+
+def masked_experts_fp8(hidden_q, hidden_s, w1, w2, w1_s, w2_s, masked_m, block_shape=(128, 128)):
+    """Experts over the masked layout (python/sglang/srt/layers/moe/moe_runner/deep_gemm.py:362-494):
+    for every expert ``e`` and row ``t < masked_m[e]``: gate_up GEMM -> SiLU*mul -> 1x128 re-quant
+    -> down GEMM, in fp32. Rows past ``masked_m[e]`` are returned as NaN (unspecified)."""
+    E, T_pad, H = hidden_q.shape
+    out = torch.full((E, T_pad, w2.shape[1]), float("nan"), dtype=torch.float32)
+    for e in range(E):
+        m = int(masked_m[e])
+        if m == 0:
+            continue
+        inter = w8a8_block_fp8_matmul(hidden_q[e, :m].to(torch.float32), w1[e], hidden_s[e, :m], w1_s[e], block_shape,
+                                      output_dtype=torch.float32)
+        act_q, act_s = per_token_group_quant_fp8(silu_and_mul(inter).contiguous(), block_shape[1])
+        out[e, :m] = w8a8_block_fp8_matmul(act_q, w2[e], act_s, w2_s[e], block_shape, output_dtype=torch.float32)
     return out
 
 

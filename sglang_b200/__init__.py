@@ -12,7 +12,13 @@ from .fp8_kernel import (  # noqa: F401
 from .moe_align_block_size import moe_align_block_size, sgl_moe_align_block_size  # noqa: F401
 
 __version__ = "0.1.0"
-from .fused_moe import MoeRunnerConfig, StandardTopKOutput, fused_experts, fused_moe  # noqa: F401,E402
+from .fused_moe import (  # noqa: F401,E402
+    MoeRunnerConfig,
+    StandardTopKOutput,
+    fused_experts,
+    fused_moe,
+    masked_fused_experts,
+)
 from .topk import (  # noqa: F401,E402
     TopKConfig,
     biased_grouped_topk,

@@ -324,7 +324,104 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   return B200_OK;
 }
 
+// ---------------------------------------------------------------- masked (low-latency) layout
+// Tokens arrive already grouped by expert: hidden [E][T_pad][H] with the first masked_m[e] rows of
+// expert e valid (what a low-latency expert-parallel dispatch delivers). The grouped GEMMs above
+// run unchanged on that layout: row tile mt belongs to expert mt / (T_pad/128) and is skipped
+// when it starts at or beyond masked_m[e]; rows past masked_m[e] inside a live tile are computed
+// and dropped by the store predicate (their "destination" is the out-of-range index).
+__global__ void __launch_bounds__(256) masked_meta_kernel(const int32_t* __restrict__ masked_m, int32_t* __restrict__ sorted,
+                                                          int32_t* __restrict__ expert_ids, int32_t* __restrict__ npp,
+                                                          int E, int64_t T_pad) {
+  const int64_t cap = (int64_t)E * T_pad;
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row == 0) *npp = (int32_t)cap;
+  if (row >= cap) return;
+  const int e = (int)(row / T_pad);
+  const int64_t r = row - (int64_t)e * T_pad;
+  const int m = min(max(masked_m[e], 0), (int)T_pad);
+  sorted[row] = r < m ? (int32_t)row : (int32_t)cap;
+  if (r % kMoeBlockM == 0) expert_ids[row / kMoeBlockM] = r < m ? e : -1;
+}
+
+struct MaskedWorkspace {
+  int64_t cap;
+  size_t off_sorted, off_expert, off_npp, off_aq2, off_as2, total;
+};
+
+static MaskedWorkspace masked_workspace_layout(int E, int64_t T_pad, int64_t I) {
+  MaskedWorkspace w = {};
+  w.cap = (int64_t)E * T_pad;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { size_t at = o; o = align_up(o + bytes, 256); return at; };
+  w.off_sorted = take((size_t)w.cap * 4);
+  w.off_expert = take((size_t)(w.cap / kMoeBlockM) * 4);
+  w.off_npp = take(4);
+  w.off_aq2 = take((size_t)w.cap * I);
+  w.off_as2 = take((size_t)w.cap * (I / 128) * 4);
+  w.total = o;
+  return w;
+}
+
+template <typename T>
+static int run_masked_experts(const void* hidden_q, const float* hidden_s, const void* w1, const void* w2,
+                              const float* w1_scale, const float* w2_scale, const int32_t* masked_m, void* out, int E,
+                              int64_t T_pad, int64_t H, int64_t I, uint8_t* ws, cudaStream_t st) {
+  const MaskedWorkspace L = masked_workspace_layout(E, T_pad, I);
+  int32_t* sorted = reinterpret_cast<int32_t*>(ws + L.off_sorted);
+  int32_t* expert_ids = reinterpret_cast<int32_t*>(ws + L.off_expert);
+  int32_t* npp = reinterpret_cast<int32_t*>(ws + L.off_npp);
+  uint8_t* aq2 = ws + L.off_aq2;
+  float* as2 = reinterpret_cast<float*>(ws + L.off_as2);
+  masked_meta_kernel<<<(unsigned)cdiv(L.cap, 256), 256, 0, st>>>(masked_m, sorted, expert_ids, npp, E, T_pad);
+  int rc = check_launch("masked_meta_kernel");
+  if (rc) return rc;
+  GemmParams p = {};
+  p.expert_ids = expert_ids; p.num_post_pad = npp; p.sorted_ids = sorted; p.numel = (int)L.cap;
+  p.M = (int)L.cap;
+  // gate_up: row-major input scales [cap][H/128]
+  p.As = hidden_s; p.as_sm = H / 128; p.as_sk = 1; p.Bs = w1_scale; p.N = (int)I; p.K = (int)H;
+  p.q_out = aq2; p.q_scales = as2; p.q_scale_ld = L.cap;
+  if ((rc = launch_gemm<GEMM_GROUPED_SILU_QUANT, T>(hidden_q, w1, (int64_t)E * 2 * I, p, 256, st, 0))) return rc;
+  // down: rows stay where they are (identity "scatter"), no router weight
+  p.As = as2; p.as_sm = 1; p.as_sk = L.cap; p.Bs = w2_scale; p.C = out; p.ldc = H; p.N = (int)H; p.K = (int)I;
+  return launch_gemm<GEMM_GROUPED_SCATTER, T>(aq2, w2, (int64_t)E * H, p, 0, st, 0);
+}
+
 }  // namespace b200
+
+extern "C" size_t b200_masked_experts_fp8_workspace_bytes(int E, int64_t T_pad, int64_t H, int64_t I) {
+  if (E <= 0 || T_pad <= 0 || H <= 0 || I <= 0) return 0;
+  return b200::masked_workspace_layout(E, T_pad, I).total;
+}
+
+extern "C" int b200_masked_experts_fp8(const void* hidden_q, const float* hidden_s, const void* w1, const void* w2,
+                                       const float* w1_scale, const float* w2_scale, const int32_t* masked_m, void* out,
+                                       int out_dtype, int E, int64_t T_pad, int64_t H, int64_t I, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(E > 0 && T_pad > 0 && H > 0 && I > 0, "masked_experts: bad shape");
+  B200_CHECK_ARG(hidden_q && hidden_s && w1 && w2 && w1_scale && w2_scale && masked_m && out, "masked_experts: null pointer");
+  B200_UNSUPPORTED(T_pad % 128 != 0, "masked_experts: T_pad=%lld must be a multiple of 128", (long long)T_pad);
+  B200_UNSUPPORTED(H % 128 != 0 || I % 128 != 0, "masked_experts: H=%lld and I=%lld must be multiples of 128",
+                   (long long)H, (long long)I);
+  B200_UNSUPPORTED((int64_t)E * T_pad >= (1LL << 30), "masked_experts: too many rows");
+  B200_CHECK_ARG(((uintptr_t)hidden_q & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w1 & 15) == 0 &&
+                     ((uintptr_t)w2 & 15) == 0, "masked_experts: tensors must be 16-byte aligned");
+  const size_t need = b200_masked_experts_fp8_workspace_bytes(E, T_pad, H, I);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0) {
+    set_error_detail("masked_experts: workspace %zu < %zu bytes or not 256-byte aligned", workspace_bytes, need);
+    return B200_E_WORKSPACE;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (out_dtype == B200_BF16)
+    return run_masked_experts<__nv_bfloat16>(hidden_q, hidden_s, w1, w2, w1_scale, w2_scale, masked_m, out, E, T_pad, H, I, ws, st);
+  if (out_dtype == B200_F16)
+    return run_masked_experts<__half>(hidden_q, hidden_s, w1, w2, w1_scale, w2_scale, masked_m, out, E, T_pad, H, I, ws, st);
+  set_error_detail("masked_experts: output dtype code %d is not bf16/f16", out_dtype);
+  return B200_E_UNSUPPORTED;
+}
 
 extern "C" size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, int E, int64_t H, int64_t I) {
   if (T <= 0 || topk <= 0 || E <= 0 || H <= 0 || I <= 0) return 0;

@@ -180,6 +180,53 @@ def fused_experts(
     )
 
 
+def masked_fused_experts(
+    hidden_states: torch.Tensor,
+    hidden_states_scale: torch.Tensor,
+    w13_weight: torch.Tensor,
+    w13_scale: torch.Tensor,
+    w2_weight: torch.Tensor,
+    w2_scale: torch.Tensor,
+    masked_m: torch.Tensor,
+    expected_m: Optional[int] = None,
+    output_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """Experts over the masked (low-latency expert-parallel) layout, the job of the reference's
+    ``DeepGemmRunnerCore._run_masked_gemm`` (moe_runner/deep_gemm.py:362-494): ``hidden_states
+    [E, T_pad, H]`` FP8 with ``hidden_states_scale [E, T_pad, H/128]`` fp32, the first
+    ``masked_m[e]`` rows of expert ``e`` valid; returns ``[E, T_pad, H]`` whose valid rows hold
+    ``down(silu(gate) * up)`` (rows past ``masked_m[e]`` are not written). ``expected_m`` is the
+    reference's scheduling hint and is not needed here."""
+    assert hidden_states.dim() == 3 and hidden_states.dtype == fp8_dtype and hidden_states.is_contiguous()
+    E, T_pad, H = hidden_states.shape
+    assert tuple(hidden_states_scale.shape) == (E, T_pad, H // 128), "hidden_states_scale shape"
+    two_i = w13_weight.shape[1]
+    I = two_i // 2
+    assert w13_weight.shape == (E, two_i, H) and w2_weight.shape == (E, H, I), "expert weight shapes"
+    assert w13_weight.dtype == fp8_dtype and w2_weight.dtype == fp8_dtype
+    assert w13_weight.is_contiguous() and w2_weight.is_contiguous()
+    assert tuple(w13_scale.shape) == (E, (two_i + 127) // 128, (H + 127) // 128), "w13_scale shape"
+    assert tuple(w2_scale.shape) == (E, (H + 127) // 128, (I + 127) // 128), "w2_scale shape"
+    assert masked_m.shape == (E,), "masked_m holds one count per local expert"
+    assert output_dtype in (torch.bfloat16, torch.float16)
+    N.require_cuda(hidden_states, hidden_states_scale, w13_weight, w2_weight, w13_scale, w2_scale, masked_m)
+    hs = hidden_states_scale.to(torch.float32).contiguous()
+    w13_scale = w13_scale.to(torch.float32).contiguous()
+    w2_scale = w2_scale.to(torch.float32).contiguous()
+    mm = masked_m.to(torch.int32).contiguous()
+    out = torch.empty((E, T_pad, H), dtype=output_dtype, device=hidden_states.device)
+    lib = N.load()
+    ws_bytes = lib.b200_masked_experts_fp8_workspace_bytes(E, T_pad, H, I)
+    with N.on_device(hidden_states):
+        ws = _workspace(hidden_states.device, ws_bytes)
+        st = lib.b200_masked_experts_fp8(
+            N.ptr(hidden_states), N.ptr(hs), N.ptr(w13_weight), N.ptr(w2_weight), N.ptr(w13_scale), N.ptr(w2_scale),
+            N.ptr(mm), N.ptr(out), N.DTYPE_CODE[output_dtype], E, T_pad, H, I, N.ptr(ws), ws_bytes, N.current_stream(),
+        )
+    N.check(st, "masked_fused_experts")
+    return out
+
+
 def fused_moe(
     hidden_states: torch.Tensor,
     w1: torch.Tensor,

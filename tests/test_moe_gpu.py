@@ -151,3 +151,42 @@ def test_deepseek_routing_skewed_load():
     ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
     out = _run(x, w1, w2, w1_s, w2_s, tw, ti)
     assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("E,T_pad,H,I,counts", [(4, 128, 256, 128, [5, 0, 128, 77]), (8, 256, 512, 256, [0, 1, 129, 256, 17, 0, 200, 64]),
+                                               (2, 384, 256, 384, [300, 130])])
+def test_masked_layout_experts(E, T_pad, H, I, counts):
+    """Low-latency layout [E, T_pad, H] with masked_m valid rows per expert: valid rows vs the fp32
+    oracle; rows past masked_m[e] are never written."""
+    import sglang_b200 as S
+
+    g = torch.Generator().manual_seed(E * 1000 + T_pad)
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 50 + E)
+    x = torch.randn(E, T_pad, H, generator=g).bfloat16()
+    xq, xs = O.per_token_group_quant_fp8(x.view(-1, H).contiguous(), 128)
+    xq, xs = xq.view(E, T_pad, H), xs.view(E, T_pad, H // 128)
+    masked_m = torch.tensor(counts, dtype=torch.int32)
+    ref = O.masked_experts_fp8(xq, xs, w1, w2, w1_s, w2_s, masked_m)
+    out = S.masked_fused_experts(xq.cuda(), xs.cuda(), w1.cuda(), w1_s.cuda(), w2.cuda(), w2_s.cuda(), masked_m.cuda())
+    _status_ok()
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (E, T_pad, H)
+    for e in range(E):
+        m = counts[e]
+        if m:
+            assert O.rel_frobenius(out[e, :m].float().cpu(), ref[e, :m]) < TOL, e
+    # untouched rows: run again into a poisoned buffer through the C ABI's view of `out`
+    from sglang_b200 import _native as N
+    from sglang_b200.fp8_kernel import _workspace
+
+    lib = N.load()
+    poison = torch.full((E, T_pad, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    nbytes = lib.b200_masked_experts_fp8_workspace_bytes(E, T_pad, H, I)
+    ws = _workspace(poison.device, nbytes)
+    args = [t.cuda() for t in (xq, xs, w1, w2, w1_s, w2_s, masked_m)]
+    st = lib.b200_masked_experts_fp8(*[N.ptr(t) for t in args], N.ptr(poison), N.BF16, E, T_pad, H, I, N.ptr(ws), nbytes,
+                                     N.current_stream())
+    N.check(st, "masked_experts")
+    torch.cuda.synchronize()
+    for e in range(E):
+        assert torch.all(poison[e, counts[e]:] == 7.0), e
+        assert torch.equal(poison[e, : counts[e]], out[e, : counts[e]])
