@@ -66,6 +66,22 @@ int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s
                                    int64_t s_stride_m, int64_t s_stride_g,
                                    float eps, int formula, void* stream);
 
+/* Same quantisation with power-of-two ("UE8M0") scales packed for MN-major consumers
+ * replaces: sglang_per_token_group_quant_fp8(..., column_major_scales=True, scale_tma_aligned=True,
+ *           scale_ue8m0=True[, fuse_silu_and_mul=True[, masked_m=...]]) (fp8_kernel.py:498-565,
+ *           :568-610) -> sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu
+ * x [M,K] (or [M,2K] = gate | up when fuse_silu_and_mul: the quantised value is T(silu(gate)) * up
+ * in the input type); q [M,K] e4m3; s_packed: int32 words, the scale of (row t, group g) is the
+ * biased exponent byte (g % 4) of word [g/4][t] of a [ceil(K/group/4)][aligned_mn] array
+ * (aligned_mn >= rows, multiple of 4); bytes past the last group are written as 0.
+ * amax is floored at 1e-10, e = ceil(log2(amax/448)), q = x * 2^-e, byte = e + 127.
+ * masked_m != NULL: x is [num_experts][M/num_experts][..], rows t >= masked_m[expert] are skipped
+ * and every expert has its own scale array (expert stride ceil(K/group/4) * aligned_mn words). */
+int b200_per_token_group_quant_fp8_ue8m0(const void* x, int x_dtype, void* q, void* s_packed,
+                                         int64_t M, int64_t K, int group, int64_t aligned_mn,
+                                         int fuse_silu_and_mul, const int32_t* masked_m,
+                                         int num_experts, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * w8a8_block_fp8_matmul
  * replaces: python/sglang/srt/layers/quantization/fp8_kernel.py:1285-1300 (Triton kernel

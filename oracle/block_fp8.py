@@ -54,6 +54,10 @@ __all__ = [
     "silu_and_mul",
     "fused_experts_fp8",
     "masked_experts_fp8",
+    "ceil_pow2",
+    "quant_weight_ue8m0",
+    "pack_ue8m0_mn_major",
+    "per_token_group_quant_fp8_ue8m0",
     "softmax_topk",
     "biased_grouped_topk",
     "sigmoid_topk",
@@ -273,6 +277,73 @@ def fused_experts_fp8(
     if routed_scaling_factor is not None:
         out = out * routed_scaling_factor
     return out
+
+
+# ------------------------------------------------------------------------------ UE8M0
+def ceil_pow2(x: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= x for positive fp32 x, computed on the bits (no log2 rounding):
+    what ``ceil_to_ue8m0`` = ``2 ** ceil(log2(x))`` means
+    (python/sglang/srt/layers/quantization/fp8_utils.py:1404-1405)."""
+    bits = x.to(torch.float32).contiguous().view(torch.int32)
+    exp = (bits >> 23) & 0xFF
+    exp = exp + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return (exp << 23).view(torch.float32)
+
+
+def quant_weight_ue8m0(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 ``[n, k]`` -> FP8 + one power-of-two fp32 scale per 128x128 block: amax clamped at
+    1e-4, ``sf = ceil_pow2(amax / 448)``, ``q = w * (1 / sf)`` with the multiply in bf16
+    (fp8_utils.py:1247-1270, 1385-1401)."""
+    assert w.dim() == 2 and w.dtype == torch.bfloat16
+    n, k = w.shape
+    nb, kb = (n + 127) // 128, (k + 127) // 128
+    q = torch.zeros(nb * 128, kb * 128, dtype=FP8)
+    sf = torch.empty(nb, kb, dtype=torch.float32)
+    wp = torch.zeros(nb * 128, kb * 128, dtype=torch.bfloat16)
+    wp[:n, :k] = w
+    for i in range(nb):
+        for j in range(kb):
+            blk = wp[i * 128 : i * 128 + 128, j * 128 : j * 128 + 128]
+            amax = blk.abs().float().amax().clamp(min=1e-4)
+            s = ceil_pow2((amax / FP8_MAX).reshape(1))[0]
+            sf[i, j] = s
+            # bf16 tensor times fp32 0-dim tensor stays bf16 in torch: one rounding to bf16, then FP8
+            q[i * 128 : i * 128 + 128, j * 128 : j * 128 + 128] = (blk * (1.0 / s)).to(FP8)
+    return q[:n, :k].contiguous(), sf
+
+
+def pack_ue8m0_mn_major(sf: torch.Tensor) -> torch.Tensor:
+    """fp32 power-of-two scales ``[mn, k]`` -> int32 ``[mn, ceil(k/4)]`` with strides
+    ``(1, align(mn, 4))``: byte ``j`` of word ``[r, c]`` is the exponent byte of ``sf[r, 4c + j]``
+    (zero past k) (fp8_utils.py:1306-1334)."""
+    mn, k = sf.shape
+    amn, kw = (mn + 3) // 4 * 4, (k + 3) // 4
+    exp = ((sf.contiguous().view(torch.int32) >> 23) & 0xFF).to(torch.int64)
+    words = torch.zeros(kw, amn, dtype=torch.int64)
+    for c in range(k):
+        words[c // 4, :mn] |= exp[:, c] << (8 * (c % 4))
+    words = torch.where(words >= 2**31, words - 2**32, words).to(torch.int32)
+    return words.t()[:mn, :]
+
+
+def per_token_group_quant_fp8_ue8m0(x: torch.Tensor, group_size: int = 128, fuse_silu_and_mul: bool = False):
+    """Activation quantisation with power-of-two scales as the reference's CUDA kernel computes it
+    (sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:56-80, 343-395): ``amax`` floored at
+    1e-10, ``e = ceil(log2(amax * (1/448)))`` on the bits, ``q = x * 2**-e``; returns the FP8
+    tensor and the fp32 scales ``2**e`` ``[.., K/g]`` (pack with ``pack_ue8m0_mn_major``).
+    ``fuse_silu_and_mul``: ``x`` is ``[.., 2K]`` = gate | up and the quantised value is
+    ``T(silu(gate)) * up`` in the input dtype ``T``. PARITY UNPINNED for this flag: on sm_100 the
+    reference evaluates silu with the hardware ``tanh.approx``; here it is the exact fp32 silu."""
+    if fuse_silu_and_mul:
+        k = x.shape[-1] // 2
+        gate, up = x[..., :k], x[..., k:]
+        act = (gate.float() * torch.sigmoid(gate.float())).to(x.dtype)
+        x = (act.float() * up.float()).to(x.dtype)  # the product of two 16-bit values is exact in fp32
+    xf = x.reshape(-1, group_size).to(torch.float32)
+    amax = xf.abs().amax(dim=-1, keepdim=True).clamp(min=1e-10)
+    sf = ceil_pow2(amax * torch.tensor(1.0 / 448.0, dtype=torch.float32))
+    q = (xf * (torch.ones_like(sf) / sf)).clamp(min=FP8_MIN, max=FP8_MAX).to(FP8).reshape(x.shape)
+    return q, sf.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
 
 
 def masked_experts_fp8(hidden_q, hidden_s, w1, w2, w1_s, w2_s, masked_m, block_shape=(128, 128)):

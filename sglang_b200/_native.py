@@ -26,6 +26,10 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int64, c_float, c_int, c_void_p],
     ),
+    "b200_per_token_group_quant_fp8_ue8m0": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_int, c_void_p],
+    ),
     "b200_w8a8_block_fp8_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "b200_w8a8_block_fp8_gemm": (
         c_int,

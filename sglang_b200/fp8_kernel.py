@@ -41,9 +41,16 @@ def create_per_token_group_quant_fp8_output_scale(
     """Scale buffer in one of the reference's layouts (fp8_kernel.py:454-495): row-major
     ``[..., M, K/g]``; column-major (same shape, strides ``(1, M)``); column-major with the
     M extent of the storage padded to a multiple of 4 ("TMA aligned")."""
-    if scale_ue8m0:
-        raise NotImplementedError("scale_ue8m0 (packed power-of-two scales) is not part of this path")
     x_shape = tuple(x_shape)
+    if scale_ue8m0:
+        # packed exponent bytes, four groups per int32, MN-major with the row extent padded to 4
+        assert column_major_scales and scale_tma_aligned
+        *x_batch, x_q_mn, x_q_k = x_shape
+        aligned_mn = ceil_align(x_q_mn, 4)
+        aligned_k = ceil_align(x_q_k // group_size, 4)
+        return torch.empty(
+            (*x_batch, aligned_k // 4, aligned_mn), device=device, dtype=torch.int32
+        ).transpose(-1, -2)[..., :x_q_mn, :]
     if column_major_scales:
         if scale_tma_aligned:
             aligned = ceil_align(x_shape[-2], 4)
@@ -71,15 +78,26 @@ def per_token_group_quant_fp8(
 
     Same contract as the reference's ``per_token_group_quant_fp8``
     (fp8_kernel.py:498-565): ``x`` contiguous with last dim divisible by ``group_size``.
-    ``enable_v2`` is accepted and ignored (one kernel here). The masked-layout,
-    fused-SiLU and UE8M0 variants raise NotImplementedError instead of silently differing.
+    ``enable_v2`` is accepted and ignored (one kernel per scale format here).
+
+    ``scale_ue8m0`` (with ``column_major_scales`` and ``scale_tma_aligned``, as the reference
+    requires): power-of-two scales packed as exponent bytes, four groups per int32, MN-major.
+    ``fuse_silu_and_mul`` (UE8M0 only, like the reference's kernel): ``x`` is ``[.., 2K]`` =
+    gate | up and ``silu(gate) * up`` is quantised. ``masked_m`` (with ``fuse_silu_and_mul``):
+    ``x`` is ``[E, T_pad, 2K]`` and only the first ``masked_m[e]`` rows of expert ``e`` are
+    processed.
     """
     assert x.shape[-1] % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`"
     assert x.is_contiguous(), "`x` is not contiguous"
-    if scale_ue8m0 or fuse_silu_and_mul or masked_m is not None:
-        raise NotImplementedError("scale_ue8m0 / fuse_silu_and_mul / masked_m are not part of this path")
     N.require_cuda(x)
     assert x.dtype in (torch.bfloat16, torch.float16, torch.float32), f"unsupported input dtype {x.dtype}"
+    if scale_ue8m0 or fuse_silu_and_mul or masked_m is not None:
+        if not scale_ue8m0:
+            raise NotImplementedError("fuse_silu_and_mul / masked_m are built for scale_ue8m0=True only")
+        if masked_m is not None and not fuse_silu_and_mul:
+            raise NotImplementedError("masked_m is built together with fuse_silu_and_mul only")
+        return _per_token_group_quant_fp8_ue8m0(x, group_size, eps, column_major_scales, scale_tma_aligned,
+                                                fuse_silu_and_mul, masked_m)
     if column_major_scales:
         assert x.dim() == 2, "column-major scales need a 2-D input"
     x_q = torch.empty_like(x, dtype=fp8_dtype)
@@ -100,6 +118,39 @@ def per_token_group_quant_fp8(
             )
         N.check(st, "per_token_group_quant_fp8")
     return x_q, x_s
+
+
+def _per_token_group_quant_fp8_ue8m0(x, group_size, eps, column_major_scales, scale_tma_aligned, fuse_silu_and_mul,
+                                     masked_m):
+    assert abs(eps - 1e-10) < 1e-13, "the power-of-two kernel floors amax at 1e-10 like the reference's"
+    assert (x.shape[-1] // (2 if fuse_silu_and_mul else 1)) % group_size == 0
+    out_shape = (*x.shape[:-1], x.shape[-1] // (2 if fuse_silu_and_mul else 1))
+    assert len(out_shape) == (3 if masked_m is not None else 2), "2-D input, or [E, T_pad, 2K] with masked_m"
+    x_q = torch.empty(out_shape, device=x.device, dtype=fp8_dtype)
+    x_s = create_per_token_group_quant_fp8_output_scale(out_shape, x.device, group_size, column_major_scales,
+                                                        scale_tma_aligned, True)
+    K = out_shape[-1]
+    rows = x_q.numel() // K if K else 0
+    if rows == 0:
+        return x_q, x_s
+    experts = out_shape[0] if masked_m is not None else 1
+    mm = None
+    if masked_m is not None:
+        assert masked_m.shape == (experts,)
+        mm = masked_m.to(device=x.device, dtype=torch.int32).contiguous()
+    with N.on_device(x):
+        st = N.load().b200_per_token_group_quant_fp8_ue8m0(
+            N.ptr(x), N.DTYPE_CODE[x.dtype], N.ptr(x_q), x_s.data_ptr(), rows, K, group_size, ceil_align(out_shape[-2], 4),
+            int(fuse_silu_and_mul), N.ptr(mm), experts, N.current_stream(),
+        )
+    N.check(st, "per_token_group_quant_fp8 (UE8M0)")
+    return x_q, x_s
+
+
+def sglang_per_token_group_quant_fp8_ue8m0(x: torch.Tensor, group_size: int, eps: float = 1e-10):
+    """The reference's shorthand (fp8_kernel.py:568-610): FP8 + packed power-of-two scales."""
+    return per_token_group_quant_fp8(x, group_size, eps, column_major_scales=True, scale_tma_aligned=True,
+                                     scale_ue8m0=True)
 
 
 sglang_per_token_group_quant_fp8 = per_token_group_quant_fp8
@@ -154,6 +205,16 @@ def w8a8_block_fp8_matmul(
     FP8 E4M3, contiguous; ``As [.., ceil(K/128)]`` fp32 with any strides (row- or
     column-major); ``Bs [ceil(N/128), ceil(K/128)]`` fp32. Only ``block_size == [128, 128]``.
     """
+    if As.dtype == torch.int32 or Bs.dtype == torch.int32:
+        # power-of-two scales packed as exponent bytes: unpack to fp32 (exact) as the reference does
+        # for its Triton path (fp8_utils.py:699-756)
+        from .weight_quant import unpack_ue8m0_rows, unpack_ue8m0_scale
+
+        if As.dtype == torch.int32:
+            As = unpack_ue8m0_rows(As.reshape(-1, As.shape[-1]), (A.shape[-1] + 127) // 128).reshape(
+                *A.shape[:-1], (A.shape[-1] + 127) // 128)
+        if Bs.dtype == torch.int32:
+            Bs = unpack_ue8m0_scale(Bs, tuple(B.shape), block_size)
     M, Nn, K, C = prepare_block_fp8_matmul_inputs(A, B, As, Bs, block_size, output_dtype)
     if list(block_size) != [128, 128]:
         raise NotImplementedError("only block_size=[128, 128] is built")

@@ -143,6 +143,39 @@ def main():
     np.savez_compressed(os.path.join(HERE, "weight_quant.npz"), **out)
     print("weight quant ok")
 
+    # ---- UE8M0 (power-of-two scales): the reference's torch functions of fp8_utils.py:1186-1410.
+    # Its layout helper imports two one-line functions from DeepGEMM, which is not installed here.
+    dg = types.ModuleType("deep_gemm")
+    dgu = types.ModuleType("deep_gemm.utils")
+    dgu.align = lambda x, a: (x + a - 1) // a * a
+    dgu.get_tma_aligned_size = lambda mn, elem: (mn + 16 // elem - 1) // (16 // elem) * (16 // elem)
+    dg.utils = dgu
+    sys.modules.setdefault("deep_gemm", dg)
+    sys.modules.setdefault("deep_gemm.utils", dgu)
+    from sglang.srt.layers.quantization import fp8_utils as FU
+
+    out = {}
+    torch.manual_seed(2)
+    w = (torch.randn(300, 520) * 0.02).bfloat16()
+    w[:128, 128:256] = 0  # an all-zero block: amax clamps at 1e-4
+    rq, rs = FU.quant_weight_ue8m0(w, [128, 128])
+    oq, os_ = O.quant_weight_ue8m0(w)
+    assert torch.equal(rq.view(torch.uint8), oq.view(torch.uint8)) and torch.equal(rs, os_)
+    x = torch.rand(1000) * 10 + 1e-6
+    assert torch.equal(FU.ceil_to_ue8m0(x), O.ceil_pow2(x))
+    sf_rows = rs.index_select(-2, torch.arange(300) // 128)
+    rp = FU._get_mn_major_tma_aligned_packed_ue8m0_tensor_torch_impl(sf_rows)
+    op = O.pack_ue8m0_mn_major(sf_rows)
+    assert rp.shape == op.shape and rp.stride() == op.stride() and torch.equal(rp, op)
+    ru = FU._unpack_ue8m0_scale_for_triton(rp.contiguous(), (300, 520), [128, 128])
+    assert torch.equal(ru, rs)
+    q0, s0 = O.block_quant_weight_fp8(w, (128, 128))
+    rrq, rrs = FU.quant_weight_ue8m0(FU.block_quant_dequant(q0, s0, [128, 128], torch.bfloat16), [128, 128])
+    for k, v in dict(w=w, q=rq, s=rs, packed=rp.contiguous(), q0=q0, s0=s0, requant_q=rrq, requant_s=rrs).items():
+        out[f"w/{k}"] = raw(v)
+    np.savez_compressed(os.path.join(HERE, "ue8m0.npz"), **out)
+    print("ue8m0 ok")
+
     # ---- MoE: inputs as in TestW8A8BlockFP8FusedMoE (seed 0), fp32 and bf16 activations
     out = {}
     for name, M, N, K, E, topk, dt in [

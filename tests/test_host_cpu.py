@@ -46,3 +46,24 @@ def test_synthetic_inputs_are_seeded_and_shaped():
     _, ids = O.softmax_topk(lg, 2, True)
     counts = torch.bincount(ids.flatten().long(), minlength=8).float()
     assert counts.max() / counts.min().clamp(min=1) > 3  # skewed load
+
+
+def test_ue8m0_weight_requant_and_scale_layout_on_cpu():
+    """Load-time helpers are plain torch: check them against the reference's vectors without a GPU."""
+    from sglang_b200 import weight_quant as W
+
+    c = load_golden("ue8m0.npz")["w"]
+    w = torch.from_numpy(c["w"]).view(torch.bfloat16)
+    q, s = W.quant_weight_ue8m0(w)
+    assert torch.equal(q.view(torch.uint8), torch.from_numpy(c["q"])) and torch.equal(s, torch.from_numpy(c["s"]))
+    packed = W.transform_scale_ue8m0(s, mn=w.shape[0])
+    assert packed.dtype == torch.int32 and packed.stride() == (1, 300)
+    assert torch.equal(packed.contiguous(), torch.from_numpy(c["packed"]))
+    assert torch.equal(W.unpack_ue8m0_scale(packed, tuple(w.shape)), s)
+    rq, rs = W.requant_weight_ue8m0(torch.from_numpy(c["q0"]).view(torch.float8_e4m3fn), torch.from_numpy(c["s0"]))
+    assert torch.equal(rq.view(torch.uint8), torch.from_numpy(c["requant_q"]))
+    assert torch.equal(W.unpack_ue8m0_scale(rs, tuple(w.shape)), torch.from_numpy(c["requant_s"]))
+    # every scale is a power of two and the re-quantised weight stays within FP8 resolution of the original
+    assert torch.all(torch.frexp(s)[0] == 0.5)
+    err = (W.block_dequant_weight(q, s) - w.float()).abs().max()
+    assert err < 0.02 * 4 / 8

@@ -116,3 +116,15 @@ def test_align_properties_and_minus_one_bucket():
 def test_ep_local_expert_ids():
     ids = torch.tensor([[0, 5], [7, 3]], dtype=torch.int32)
     assert O.ep_local_expert_ids(ids, 8, 2, 1).tolist() == [[-1, 1], [3, -1]]
+
+
+def test_ue8m0_weight_side_matches_reference_vectors():
+    c = load_golden("ue8m0.npz")["w"]
+    w = torch.from_numpy(c["w"]).view(torch.bfloat16)
+    q, s = O.quant_weight_ue8m0(w)
+    assert torch.equal(q.view(torch.uint8), torch.from_numpy(c["q"])) and torch.equal(s, torch.from_numpy(c["s"]))
+    rows = s.index_select(-2, torch.arange(w.shape[0]) // 128)
+    packed = O.pack_ue8m0_mn_major(rows)
+    assert torch.equal(packed.contiguous(), torch.from_numpy(c["packed"])) and packed.stride() == (1, w.shape[0])
+    x = torch.tensor([1.0, 1.5, 2.0, 3e-5, 448.0, 0.75])
+    assert O.ceil_pow2(x).tolist() == [1.0, 2.0, 2.0, 2.0**-15, 512.0, 1.0]
