@@ -13,5 +13,9 @@ the reference calls ``torch.topk(..., sorted=False)`` (order of the k results an
 unspecified) the routing functions here return descending order with the lower index first
 on ties, the rule of the reference's CUDA routing kernels; those vectors are compared by
 expert id.
+
+Evaluate it on CPU tensors. The functions run on CUDA tensors too, but there torch divides by a
+Python scalar through its reciprocal (``amax / 448`` becomes ``amax * (1/448)``), which is not
+the arithmetic restated here and moves FP8 ties.
 """
 from .block_fp8 import *  # noqa: F401,F403

@@ -98,7 +98,7 @@ def per_token_group_quant_fp8(
         s = amax / FP8_MAX
         q = xf * (torch.ones_like(s) / s)
     elif formula == 2:
-        s = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32)
+        s = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32, device=amax.device)
         # tensor / tensor: one IEEE division, as `MAX / amax` in the kernel (a Python scalar
         # divided by a tensor would be reciprocal-then-multiply, i.e. rounded twice)
         q = xf * (torch.full_like(amax, FP8_MAX) / amax)
@@ -153,7 +153,7 @@ def w8a8_block_fp8_matmul(
     out_shape = A.shape[:-1] + (N,)
     A = A.reshape(M, K)
     As = As.reshape(M, kt).to(torch.float32)
-    C = torch.zeros(M, N, dtype=torch.float32)
+    C = torch.zeros(M, N, dtype=torch.float32, device=A.device)
     for i in range(kt):
         a = A[:, i * bk : min((i + 1) * bk, K)]
         for j in range(nt):
@@ -253,7 +253,7 @@ def fused_experts_fp8(
     if apply_router_weight_on_input:
         assert topk == 1
     a_rep = a.view(T, 1, D).repeat(1, topk, 1).reshape(-1, D)
-    out = torch.zeros(T * topk, w2.shape[1], dtype=compute_dtype)
+    out = torch.zeros(T * topk, w2.shape[1], dtype=compute_dtype, device=a.device)
     ids = topk_ids.reshape(-1)
     a_q, a_s = per_token_group_quant_fp8(a_rep.contiguous(), bk)
     a_q = a_q.to(torch.float32)

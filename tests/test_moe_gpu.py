@@ -190,3 +190,48 @@ def test_masked_layout_experts(E, T_pad, H, I, counts):
     for e in range(E):
         assert torch.all(poison[e, counts[e]:] == 7.0), e
         assert torch.equal(poison[e, : counts[e]], out[e, : counts[e]])
+
+
+@pytest.mark.parametrize("name,T,E,topk,H,I", [("mixtral", 8192, 8, 2, 4096, 14336), ("deepseek_v3", 16384, 256, 8, 7168, 2048)])
+def test_full_size_layer_properties(name, T, E, topk, H, I):
+    """The layers at the sizes the benchmark runs. The whole layer is too big for the CPU oracle,
+    so: (a) a token's result does not depend on the other tokens, hence a few sampled rows of the
+    full run are compared with the oracle evaluated on those tokens alone; (b) doubling the router weights doubles the output exactly;
+    (c) permuting the tokens permutes the output rows."""
+    import sglang_b200 as S
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(77)
+    fp8 = torch.float8_e4m3fn
+    w1 = torch.empty(E, 2 * I, H, dtype=fp8, device=dev)
+    w2 = torch.empty(E, H, I, dtype=fp8, device=dev)
+    for e in range(E):  # per expert: bounded temporary memory
+        w1[e] = (torch.randn(2 * I, H, device=dev, generator=g) * 60).clamp(-448, 448).to(fp8)
+        w2[e] = (torch.randn(H, I, device=dev, generator=g) * 60).clamp(-448, 448).to(fp8)
+    w1_s = torch.rand(E, 2 * I // 128, H // 128, device=dev, generator=g) * 2e-4 + 1e-4
+    w2_s = torch.rand(E, H // 128, I // 128, device=dev, generator=g) * 2e-4 + 1e-4
+    x = torch.randn(T, H, device=dev, generator=g).bfloat16()
+    logits = torch.randn(T, E, device=dev, generator=g)
+    if name == "deepseek_v3":
+        tw, ti = S.biased_grouped_topk(x, logits, torch.zeros(E, device=dev), topk, True, 8, 4)
+    else:
+        tw, ti = S.fused_topk(x, logits, topk, True)
+    cfg = S.MoeRunnerConfig(inplace=False)
+
+    def run(x_, tw_, ti_):
+        return S.fused_experts(x_, w1, w2, S.StandardTopKOutput(tw_, ti_, None), cfg, use_fp8_w8a8=True,
+                               w1_scale=w1_s, w2_scale=w2_s, block_shape=[128, 128])
+
+    out = run(x, tw, ti)
+    _status_ok()
+    # the oracle runs on the CPU (on a CUDA tensor torch divides by a Python scalar through its
+    # reciprocal, which is not the arithmetic being restated): a few rows, only the experts they use
+    rows = torch.randperm(T, device=dev, generator=g)[: (16 if E <= 8 else 6)]
+    used = torch.unique(ti[rows].flatten()).long()
+    local = torch.searchsorted(used, ti[rows].long()).to(torch.int32)
+    ref = O.fused_experts_fp8(x[rows].cpu(), w1[used].cpu(), w2[used].cpu(), w1_s[used].cpu(), w2_s[used].cpu(),
+                              tw[rows].cpu(), local.cpu(), [128, 128])
+    assert O.rel_frobenius(out[rows].float().cpu(), ref) < TOL
+    assert torch.equal(run(x, tw * 2, ti), out * 2)
+    perm = torch.randperm(T, device=dev, generator=g)
+    assert torch.equal(run(x[perm].contiguous(), tw[perm].contiguous(), ti[perm].contiguous()), out[perm])
