@@ -72,6 +72,13 @@ __device__ __forceinline__ void mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, ui
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// one commit that arrives on the barrier at the same shared-memory offset in every CTA of `mask`
+// (tcgen05.commit is the one multicast form used anywhere in this library; no data is moved)
+__device__ __forceinline__ void mma_commit_pair_multicast(uint32_t bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
+}
 }  // namespace ptx
 
 struct Pair {
@@ -188,10 +195,9 @@ block_fp8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
             const uint32_t d = tmem_base + b * BN;
 #pragma unroll
             for (int k = 0; k < kBK / 32; ++k) ptx::mma_f8_pair(d, da + 2 * k, db + 2 * k, idesc, k > 0);
-            // partial product ready: one commit per CTA (no multicast form). Each CTA's promotion
-            // warp 0 releases its own shared-memory stage when it sees the barrier.
-            ptx::mma_commit_pair(ptx::mapa(tfull_bar(b), 0));
-            ptx::mma_commit_pair(ptx::mapa(tfull_bar(b), 1));
+            // partial product ready: one commit, delivered to the tfull barrier of both CTAs. Each
+            // CTA's promotion warp 0 releases its own shared-memory stage when it sees the barrier.
+            ptx::mma_commit_pair_multicast(tfull_bar(b), (uint16_t)3);
           }
           __syncwarp();
         }
