@@ -149,8 +149,12 @@ int b200_moe_align_block_size_static(const void* topk_ids, int ids_dtype, int64_
  * topk_weights fp32 [T,topk], topk_ids int32 [T,topk] with values in [-1,E) (-1 = expert
  * not on this rank: contributes 0). out [T,H] (or [T,topk,H] when no_combine != 0), h_dtype;
  * out may alias a 16-bit hidden (the reference's inplace=True). H % 128 == 0, I % 128 == 0.
+ * no_combine: B200_COMBINE_SUM (0) sums the slots; B200_COMBINE_NONE (1) returns [T,topk,H];
+ * B200_COMBINE_SUM_SKIP_UNROUTED (2) sums the slots but leaves rows without any valid id unwritten
+ * (the expert-parallel receive area, where most positions belong to other ranks).
  * routed_scaling_factor multiplies the combined output (pass 1.0f for none).
  * workspace: b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I) bytes, 256-B aligned. */
+enum { B200_COMBINE_SUM = 0, B200_COMBINE_NONE = 1, B200_COMBINE_SUM_SKIP_UNROUTED = 2 };
 size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, int E, int64_t H, int64_t I);
 int b200_fused_experts_fp8(const void* hidden, const float* hidden_scale, int h_dtype,
                            const void* w1, const void* w2,

@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) moe_gather_fp8_kernel(
 template <typename T>
 __global__ void __launch_bounds__(256) moe_sum_reduce_kernel(const T* __restrict__ y, const int32_t* __restrict__ topk_ids,
                                                              T* __restrict__ out, int64_t T_tokens, int topk, int E,
-                                                             int64_t H, float scale) {
+                                                             int64_t H, float scale, int skip_unrouted) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int vec_per_row = (int)(H / 8);
   if (c >= T_tokens * vec_per_row) return;
@@ -129,14 +129,17 @@ __global__ void __launch_bounds__(256) moe_sum_reduce_kernel(const T* __restrict
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  bool any = false;
   for (int j = 0; j < topk; ++j) {
     const int e = topk_ids[t * topk + j];
     if (e < 0 || e >= E) continue;
+    any = true;
     const uint4 r = ld_nc_16(y + (t * topk + j) * H + v * 8);
     const T* h = reinterpret_cast<const T*>(&r);
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
   }
+  if (!any && skip_unrouted) return;  // a row no local expert serves: nobody reads it
   uint4 o;
   T* oh = reinterpret_cast<T*>(&o);
 #pragma unroll
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(256) moe_sum_reduce_splits_kernel(const float*
                                                                     const int32_t* __restrict__ topk_ids,
                                                                     T* __restrict__ out, int64_t rows, int slots,
                                                                     int splits, int64_t split_stride, int E, int64_t H,
-                                                                    float scale) {
+                                                                    float scale, int skip_unrouted) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int vec_per_row = (int)(H / 8);
   if (c >= rows * vec_per_row) return;
@@ -161,9 +164,11 @@ __global__ void __launch_bounds__(256) moe_sum_reduce_splits_kernel(const float*
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  bool any = false;
   for (int j = 0; j < slots; ++j) {
     const int e = topk_ids[r * slots + j];
     if (e < 0 || e >= E) continue;
+    any = true;
     for (int sp = 0; sp < splits; ++sp) {
       const float* src = y + sp * split_stride + (r * slots + j) * H + v * 8;
       const uint4 a = ld_nc_16(src), b = ld_nc_16(src + 4);
@@ -173,6 +178,7 @@ __global__ void __launch_bounds__(256) moe_sum_reduce_splits_kernel(const float*
       acc[6] += __uint_as_float(b.z); acc[7] += __uint_as_float(b.w);
     }
   }
+  if (!any && skip_unrouted) return;
   uint4 o;
   T* oh = reinterpret_cast<T*>(&o);
 #pragma unroll
@@ -233,8 +239,10 @@ static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, 
 template <typename T>
 static int run_fused_experts(const void* hidden, const float* hidden_scale, const void* w1, const void* w2, const float* w1_scale,
                              const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
-                             int64_t T_tokens, int topk, int E, int64_t H, int64_t I, int no_combine,
+                             int64_t T_tokens, int topk, int E, int64_t H, int64_t I, int combine_mode,
                              int weight_on_input, float routed_scale, uint8_t* ws, cudaStream_t st) {
+  const int no_combine = combine_mode == B200_COMBINE_NONE;
+  const int skip_unrouted = combine_mode == B200_COMBINE_SUM_SKIP_UNROUTED;
   const MoeWorkspace L = moe_workspace_layout(T_tokens, topk, E, H, I);
   const int64_t numel = T_tokens * topk;
   int32_t* sorted = reinterpret_cast<int32_t*>(ws + L.off_sorted);
@@ -311,14 +319,14 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
     const int64_t total = rows * (H / 8);
     moe_sum_reduce_splits_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
         reinterpret_cast<const float*>(c3), topk_ids, static_cast<T*>(out), rows, no_combine ? 1 : topk, down_splits,
-        numel * H, E, H, no_combine ? 1.0f : routed_scale);
+        numel * H, E, H, no_combine ? 1.0f : routed_scale, skip_unrouted);
     return check_launch("moe_sum_reduce_splits");
   }
   if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, T>(aq2, w2, (int64_t)E * H, p, force_bn, st, tiles_hint))) return rc;
   if (!no_combine) {
     const int64_t total = T_tokens * (H / 8);
     moe_sum_reduce_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(c3, topk_ids, static_cast<T*>(out), T_tokens,
-                                                                        topk, E, H, routed_scale);
+                                                                        topk, E, H, routed_scale, skip_unrouted);
     if ((rc = check_launch("moe_sum_reduce"))) return rc;
   }
   return B200_OK;
@@ -445,6 +453,7 @@ extern "C" int b200_fused_experts_fp8(const void* hidden, const float* hidden_sc
   B200_UNSUPPORTED(E + 1 > 1025, "fused_experts: more than 1024 experts");
   B200_UNSUPPORTED(T * topk >= (1LL << 30), "fused_experts: too many (token, slot) pairs");
   B200_CHECK_ARG(!apply_router_weight_on_input || topk == 1, "apply_router_weight_on_input needs topk == 1");
+  B200_CHECK_ARG(no_combine >= 0 && no_combine <= 2, "fused_experts: unknown combine mode %d", no_combine);
   B200_CHECK_ARG(((uintptr_t)hidden & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w1 & 15) == 0 &&
                      ((uintptr_t)w2 & 15) == 0, "fused_experts: tensors must be 16-byte aligned");
   const size_t need = b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I);

@@ -64,11 +64,13 @@ def fused_experts_impl(
     hidden_states_scale: Optional[torch.Tensor] = None,
     output_dtype: Optional[torch.dtype] = None,
     out: Optional[torch.Tensor] = None,
+    skip_unrouted_rows: bool = False,
 ) -> torch.Tensor:
     """Checks of the reference's ``fused_experts_impl`` (fused_moe.py:824-834) + the launch.
 
     ``out`` (extension): a preallocated contiguous result tensor, e.g. a region of peer-mapped
-    memory that other ranks read.
+    memory that other ranks read. ``skip_unrouted_rows`` (extension): rows none of whose ids is valid
+    are left unwritten instead of being zeroed.
 
     ``hidden_states_scale`` (extension used by the expert-parallel all-to-all path): when given,
     ``hidden_states`` is already FP8 E4M3 ``[T, H]`` with row-major fp32 1x128 scales
@@ -122,7 +124,8 @@ def fused_experts_impl(
         ws = _workspace(hidden_states.device, ws_bytes)
         st = lib.b200_fused_experts_fp8(
             N.ptr(hidden_states), N.ptr(hidden_states_scale), N.DTYPE_CODE[out_dtype], N.ptr(w1), N.ptr(w2), N.ptr(w1_scale),
-            N.ptr(w2_scale), N.ptr(topk_weights), N.ptr(topk_ids), N.ptr(out), T, topk, E, H, I, int(no_combine),
+            N.ptr(w2_scale), N.ptr(topk_weights), N.ptr(topk_ids), N.ptr(out), T, topk, E, H, I,
+            1 if no_combine else (2 if skip_unrouted_rows else 0),
             int(apply_router_weight_on_input),
             1.0 if routed_scaling_factor is None else float(routed_scaling_factor), N.ptr(ws), ws_bytes,
             N.current_stream(),

@@ -279,7 +279,7 @@ class FusedMoE:
 
             def experts(q, s, w, ids, out):
                 fused_experts_impl(q, self.w1, self.w2, w, ids, self.w1_s, self.w2_s, inplace=False,
-                                   hidden_states_scale=s, output_dtype=out.dtype, out=out)
+                                   hidden_states_scale=s, output_dtype=out.dtype, out=out, skip_unrouted_rows=True)
 
             return self._peer.forward(hidden_states, topk_weights, topk_ids, experts)
         from .fp8_kernel import per_token_group_quant_fp8

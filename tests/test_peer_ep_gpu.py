@@ -62,7 +62,7 @@ def test_dispatch_experts_combine_emulated_ranks(p, E, k, H, I, T_max, tokens):
         lo = d * per
         fused_experts_impl(q[d].view(torch.float8_e4m3fn), w1[lo : lo + per].cuda(), w2[lo : lo + per].cuda(), w[d], ids[d],
                            w1_s[lo : lo + per].cuda(), w2_s[lo : lo + per].cuda(), hidden_states_scale=s[d],
-                           output_dtype=torch.bfloat16, out=out[d])
+                           output_dtype=torch.bfloat16, out=out[d], skip_unrouted_rows=True)
     for r in range(p):
         T = tokens[r]
         res = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
