@@ -95,12 +95,20 @@ __global__ void __launch_bounds__(128) ep_combine_kernel(const EpCombineParams a
   const int64_t slot = (int64_t)a.rank * a.T_max + t;
   T* out = static_cast<T*>(a.out) + t * a.H;
   for (int64_t c = threadIdx.x * 8; c < a.H; c += blockDim.x * 8) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int d = 0; d < a.p; ++d) {
-      if (!s_need[d]) continue;
+    // all owners' rows are requested before any is used: the peer loads overlap instead of
+    // paying one NVLink round trip after the other
+    uint4 v[kEpMaxRanks];
+#pragma unroll
+    for (int d = 0; d < kEpMaxRanks; ++d) {
+      v[d] = make_uint4(0, 0, 0, 0);
       // written by another GPU's kernels: L2-only load (no stale L1 line of an earlier call)
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.peer_out[d]) + slot * a.H + c));
-      const T* h = reinterpret_cast<const T*>(&v);
+      if (d < a.p && s_need[d])
+        v[d] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.peer_out[d]) + slot * a.H + c));
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < kEpMaxRanks; ++d) {  // ascending rank; a rank that is not needed contributes +0
+      const T* h = reinterpret_cast<const T*>(&v[d]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
     }

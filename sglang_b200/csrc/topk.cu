@@ -34,6 +34,12 @@ struct RouteParams {
 
 constexpr float kNegInf = -__builtin_huge_valf();
 
+// float -> uint32 whose unsigned order is the float order (-inf lowest)
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 // (a, b) = two largest of {a, b, c, d}, a >= b, given a >= b and c >= d
 __device__ __forceinline__ void merge_top2(float& a, float& b, float c, float d) {
   const float hi = fmaxf(a, c);
@@ -148,15 +154,14 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
         bi = e0 + j;
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(full, bv, o);
-      const int oi = __shfl_xor_sync(full, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
+    // warp argmax in three instructions: redux.sync max over order-preserving integer keys, a
+    // ballot of the lanes that hold the maximum, and the lowest such lane wins (lanes own
+    // ascending expert ranges and each lane already kept its lowest index, so this is the
+    // lowest expert index among equal values)
+    const uint32_t key = ordered_key(bv);
+    const uint32_t kmax = __reduce_max_sync(full, key);
+    const int winner = __ffs(__ballot_sync(full, key == kmax)) - 1;
+    bi = __shfl_sync(full, bi, winner);
     // the owner hands out the unbiased score and retires the expert
     const int owner = bi / vpl, slot = bi - owner * vpl;
     float wv = 0.f;

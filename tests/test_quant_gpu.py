@@ -85,7 +85,9 @@ def test_empty_and_errors():
         S.per_token_group_quant_fp8(torch.zeros(2, 200, dtype=torch.bfloat16, device="cuda"), 128)
     with pytest.raises(AssertionError):
         S.per_token_group_quant_fp8(torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda").t(), 128)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(AssertionError):  # power-of-two scales need the column-major TMA-aligned layout, as in the reference
         S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16, device="cuda"), 128, scale_ue8m0=True)
+    with pytest.raises(NotImplementedError):  # fused SiLU is built for power-of-two scales only
+        S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16, device="cuda"), 128, fuse_silu_and_mul=True)
     with pytest.raises(RuntimeError):
         S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16), 128)
