@@ -29,3 +29,4 @@ from .topk import (  # noqa: F401,E402
     topk_sigmoid,
     topk_softmax,
 )
+from . import fp8  # noqa: F401,E402

@@ -28,7 +28,9 @@ def block_quant_weight_fp8(w: torch.Tensor, block: Sequence[int] = (128, 128)) -
     nb, kb = wf.shape[0] // bn, wf.shape[1] // bk
     blocks = wf.view(nb, bn, kb, bk).permute(0, 2, 1, 3)
     amax = blocks.abs().amax(dim=(-2, -1), keepdim=True)
-    scales = amax / FP8_MAX
+    # tensor / tensor: on a CUDA device torch turns division by a Python scalar into a multiplication by
+    # its reciprocal, which rounds differently from the division the reference performs on the CPU
+    scales = amax / torch.full_like(amax, FP8_MAX)
     scales = torch.where(scales == 0, torch.ones_like(scales), scales)
     q = (blocks / scales).to(torch.float8_e4m3fn).permute(0, 2, 1, 3).reshape(nb * bn, kb * bk)
     return q[:N, :K].contiguous(), scales.view(nb, kb).contiguous()
@@ -66,7 +68,7 @@ def per_block_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     x_padded[:m, :n] = x
     x_view = x_padded.view(-1, 128, x_padded.size(1) // 128, 128)
     x_amax = x_view.abs().float().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
-    sf = ceil_to_ue8m0(x_amax / 448.0)
+    sf = ceil_to_ue8m0(x_amax / torch.full_like(x_amax, 448.0))  # tensor / tensor: a true division on every device
     x_scaled = (x_view * (1.0 / sf)).to(torch.float8_e4m3fn)
     return x_scaled.view_as(x_padded)[:m, :n].contiguous(), sf.view(x_view.size(0), x_view.size(2))
 
