@@ -227,6 +227,9 @@ int b200_route_topk(const void* logits, int logits_dtype, const float* correctio
  * reduced and the results are written to out[0..n_ranks) and residual_out[0..n_ranks) (every
  * rank's buffers; `out` and `residual_out` are HOST arrays of device pointers, NULL = none), followed
  * by a second handshake so that on return (in stream order) every rank's output is complete.
+ * out_multicast / residual_out_multicast (by_tile only, may be NULL): an NVSwitch multicast address
+ * that maps all ranks' output buffers; results are then written once with multimem.st and
+ * replicated by the switch instead of being stored to every out[d].
  * epoch == 0 selects device-side epochs (a counter next to the flags, flags[16..18], advanced by
  * the kernels themselves): the identical call can then be replayed from a CUDA graph; a flag array
  * is driven either by host epochs or by device epochs, never both. The flag array is 32 uint32.
@@ -241,7 +244,8 @@ int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* o
                           int64_t M, int64_t N,
                           int n_ranks, int rank, int by_tile, const void* residual,
                           void* const* residual_out, const void* rms_weight, float eps, void* my_flags,
-                          void* const* peer_flags, uint32_t epoch, void* stream);
+                          void* const* peer_flags, uint32_t epoch, void* out_multicast,
+                          void* residual_out_multicast, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Expert-parallel token exchange over peer memory (dispatch / combine around fused_experts)

@@ -61,7 +61,7 @@ SIGNATURES = {
     "b200_allreduce_finish": (
         c_int,
         [c_void_p, c_int64, POINTER(c_void_p), c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p,
-         POINTER(c_void_p), c_void_p, c_float, c_void_p, POINTER(c_void_p), c_uint32, c_void_p],
+         POINTER(c_void_p), c_void_p, c_float, c_void_p, POINTER(c_void_p), c_uint32, c_void_p, c_void_p, c_void_p],
     ),
     "b200_masked_experts_fp8_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int64]),
     "b200_masked_experts_fp8": (

@@ -29,6 +29,11 @@ struct AllReduceParams {
   void* out[kMaxRanks];       // one-shot: out[0] (local). two-shot: out[d] = rank d's output buffer
   const void* residual;       // [M, N] or null
   void* residual_out[kMaxRanks];  // like out: [M, N] buffers for sum + residual, or null (may alias residual)
+  // two-shot with NVSwitch multicast: one address that maps every rank's output buffer; a
+  // multimem.st to it is replicated by the switch, so the owner sends each result once instead
+  // of once per rank. Null: plain peer stores to out[d] / residual_out[d].
+  void* out_mc;
+  void* residual_out_mc;
   const void* rms_weight;     // [N] or null
   uint32_t* my_flags;         // local [2][kMaxRanks]
   uint32_t* peer_flags[kMaxRanks];
@@ -48,6 +53,12 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// 16 bytes to every replica of a multicast address (no data conversion: the type only sizes it)
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -140,10 +151,15 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
       T* oh = reinterpret_cast<T*>(&o);
 #pragma unroll
       for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i]);
-      if (p.residual_out[0] != nullptr)
-        for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.residual_out[d]) + row * N + c) = o;
+      if (p.residual_out[0] != nullptr) {
+        if (p.residual_out_mc != nullptr) multimem_st_16(static_cast<T*>(p.residual_out_mc) + row * N + c, o);
+        else
+          for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.residual_out[d]) + row * N + c) = o;
+      }
       if (w == nullptr) {
-        for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+        if (p.out_mc != nullptr) multimem_st_16(static_cast<T*>(p.out_mc) + row * N + c, o);
+        else
+          for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss += acc[i] * acc[i];
@@ -180,7 +196,9 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
         T* oh = reinterpret_cast<T*>(&o);
 #pragma unroll
         for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * inv * to_f32<T>(wh[i]));
-        for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+        if (p.out_mc != nullptr) multimem_st_16(static_cast<T*>(p.out_mc) + row * N + c, o);
+        else
+          for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
       }
     }
   }
@@ -201,7 +219,7 @@ __global__ void __launch_bounds__(32) allreduce_results_landed_kernel(const AllR
 extern "C" int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* out, int dtype, int64_t M, int64_t N, int n_ranks,
                                      int rank, int by_tile, const void* residual, void* const* residual_out,
                                      const void* rms_weight, float eps, void* my_flags, void* const* peer_flags,
-                                     uint32_t epoch, void* stream) {
+                                     uint32_t epoch, void* out_multicast, void* residual_out_multicast, void* stream) {
   using namespace b200;
   B200_CHECK_ARG(M >= 0 && N > 0 && n_ranks >= 1 && n_ranks <= kMaxRanks && rank >= 0 && rank < n_ranks,
                  "allreduce_finish: bad shape M=%lld N=%lld ranks=%d rank=%d", (long long)M, (long long)N, n_ranks, rank);
@@ -220,6 +238,12 @@ extern "C" int b200_allreduce_finish(const void* slots, int64_t slot_stride, voi
   p.slots = slots; p.slot_stride = slot_stride; p.residual = residual; p.rms_weight = rms_weight;
   p.my_flags = static_cast<uint32_t*>(my_flags); p.M = M; p.N = N; p.n_ranks = n_ranks; p.rank = rank;
   p.by_tile = by_tile != 0; p.epoch = epoch; p.eps = eps; p.wait_ns = peer_wait_ns();
+  if (p.by_tile) {  // multicast only replaces the fan-out of the two-shot mode
+    B200_CHECK_ARG(((uintptr_t)out_multicast & 15) == 0 && ((uintptr_t)residual_out_multicast & 15) == 0,
+                   "allreduce_finish: unaligned multicast address");
+    p.out_mc = out_multicast;
+    p.residual_out_mc = residual_out != nullptr ? residual_out_multicast : nullptr;
+  }
   p.status = device_status_word();
   if (!p.status) {
     set_error_detail("cannot resolve the device status word");

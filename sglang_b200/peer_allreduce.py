@@ -41,10 +41,14 @@ class PeerAllReduce:
     rows and exactly ``n`` columns, dtype bf16 or fp16."""
 
     def __init__(self, max_tokens: int, n: int, dtype: torch.dtype = torch.bfloat16, group=None,
-                 two_shot: Optional[bool] = None, graph_safe: bool = False):
+                 two_shot: Optional[bool] = None, graph_safe: bool = False, multicast: Optional[bool] = None):
         """``graph_safe``: calls can be captured in a CUDA graph and replayed. Epochs then live on
         the device (advanced by the kernels), one slot buffer is used instead of two, and the
-        one-shot mode ends with a second handshake ("I have read my slots") that orders the reuse."""
+        one-shot mode ends with a second handshake ("I have read my slots") that orders the reuse.
+        ``multicast`` (two-shot only; default: use it when the allocation has an NVSwitch multicast
+        mapping): the owner of a row block writes its result once to the multicast address
+        (``multimem.st``) and the switch replicates it into every rank's output, instead of one peer
+        store per rank."""
         import torch.distributed._symmetric_memory as symm
 
         assert dist.is_initialized(), "torch.distributed must be initialised (one process per GPU, NCCL)"
@@ -68,6 +72,9 @@ class PeerAllReduce:
         self.buf = symm.empty(total, dtype=torch.uint8, device=dev)
         self.handle = symm.rendezvous(self.buf, self.group)
         self.base = [int(p) for p in self.handle.buffer_ptrs]
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_base = mc if (self.two_shot and mc and multicast is not False) else 0
+        assert not (multicast and self.two_shot and not mc), "this allocation has no multicast mapping"
         self.buf[self.off_flags:].zero_()
         torch.cuda.synchronize(dev)
         dist.barrier(self.group)  # every rank's flags are zero before anyone signals
@@ -136,7 +143,9 @@ class PeerAllReduce:
             st = lib.b200_allreduce_finish(
                 self._slot_ptr(self.rank, parity, 0), self.slot_elems, outs, code, m, n, self.world, self.rank, int(self.two_shot),
                 N.ptr(residual), res_outs, N.ptr(rms_weight), float(eps), self.base[self.rank] + self.off_flags,
-                self._peer_flags, epoch_arg, stream,
+                self._peer_flags, epoch_arg,
+                self.mc_base + self.off_out if self.mc_base else None,
+                self.mc_base + self.off_out + self.slot_elems * 2 if self.mc_base else None, stream,
             )
             N.check(st, "allreduce_finish")
             if self.graph_safe and not self.two_shot:

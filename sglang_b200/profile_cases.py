@@ -92,8 +92,8 @@ def main(argv) -> int:
         peers = (ctypes.c_void_p * 1)(flags.data_ptr())
         for i in range(calls(2)):
             N.check(lib.b200_allreduce_finish(slot.data_ptr(), M * Nn, outs, N.BF16, M, Nn, 1, 0, 0, resid.data_ptr(),
-                                              res_outs, gamma.data_ptr(), 1e-6, flags.data_ptr(), peers, i + 1,
-                                              N.current_stream()), "allreduce_finish")
+                                              res_outs, gamma.data_ptr(), 1e-6, flags.data_ptr(), peers, i + 1, None,
+                                              None, N.current_stream()), "allreduce_finish")
     else:
         print(__doc__)
         return 2

@@ -90,7 +90,7 @@ def test_finish_kernel_single_rank_sum_residual_rmsnorm(M, N, mode):
     for epoch in (1, 2, 3):  # flags persist: epochs must keep working call after call
         res_outs = (ctypes.c_void_p * 1)(res_out.data_ptr()) if res_out is not None else None
         st = lib.b200_allreduce_finish(slot.data_ptr(), M * N, outs, N_.BF16, M, N, 1, 0, 0, N_.ptr(residual),
-                                       res_outs, N_.ptr(w), 1e-6, flags.data_ptr(), peers, epoch,
+                                       res_outs, N_.ptr(w), 1e-6, flags.data_ptr(), peers, epoch, None, None,
                                        N_.current_stream())
         N_.check(st, "finish")
     torch.cuda.synchronize()
@@ -123,7 +123,7 @@ def test_device_epochs_replay_from_a_cuda_graph_single_rank():
     with torch.cuda.stream(s):
         def call():
             st = lib.b200_allreduce_finish(slot.data_ptr(), M * N, outs, N_.BF16, M, N, 1, 0, 0, None, None, None, 1e-6,
-                                           flags.data_ptr(), peers, 0, N_.current_stream())
+                                           flags.data_ptr(), peers, 0, None, None, N_.current_stream())
             N_.check(st, "finish")
             N_.check(lib.b200_peer_handshake(flags.data_ptr(), peers, 1, 0, 1, 0, N_.current_stream()), "handshake")
         call()
@@ -175,9 +175,12 @@ def _worker(rank, world, port, results):
         layer_x = x[:, rank * kl : (rank + 1) * kl].contiguous().cuda()
         layer_ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
         got = {}
-        for two_shot in (False, True):
-            par = PeerAllReduce(512, Nn, torch.bfloat16, two_shot=two_shot)
-            tag = "two" if two_shot else "one"
+        for two_shot, multicast, tag in ((False, None, "one"), (True, False, "two"), (True, True, "two_mc")):
+            try:
+                par = PeerAllReduce(512, Nn, torch.bfloat16, two_shot=two_shot, multicast=multicast)
+            except AssertionError:  # no NVSwitch multicast mapping on this box: the peer-store path is the test
+                assert multicast
+                continue
             dist.barrier()
             for rep, (M, xl, ref, acc, normed) in enumerate(cases):
                 out, _ = par.linear_bf16_input(xl, wl, wsl)
