@@ -25,6 +25,7 @@ rewrites them.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -45,8 +46,9 @@ class PeerAllReduce:
         """``graph_safe``: calls can be captured in a CUDA graph and replayed. Epochs then live on
         the device (advanced by the kernels), one slot buffer is used instead of two, and the
         one-shot mode ends with a second handshake ("I have read my slots") that orders the reuse.
-        ``multicast`` (two-shot only; default: use it when the allocation has an NVSwitch multicast
-        mapping): the owner of a row block writes its result once to the multicast address
+        ``multicast`` (two-shot only; default off, or ``B200_PEER_MULTICAST=1``; needs an allocation
+        with an NVSwitch multicast mapping): the owner of a row block writes its result once to the
+        multicast address
         (``multimem.st``) and the switch replicates it into every rank's output, instead of one peer
         store per rank."""
         import torch.distributed._symmetric_memory as symm
@@ -73,7 +75,9 @@ class PeerAllReduce:
         self.handle = symm.rendezvous(self.buf, self.group)
         self.base = [int(p) for p in self.handle.buffer_ptrs]
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        self.mc_base = mc if (self.two_shot and mc and multicast is not False) else 0
+        if multicast is None:
+            multicast = os.environ.get("B200_PEER_MULTICAST", "0") == "1" and bool(mc)
+        self.mc_base = mc if (self.two_shot and mc and multicast) else 0
         assert not (multicast and self.two_shot and not mc), "this allocation has no multicast mapping"
         self.buf[self.off_flags:].zero_()
         torch.cuda.synchronize(dev)
