@@ -93,3 +93,40 @@ def test_handshake_with_itself_and_argument_checks():
     assert flags[0].item() == 3 and flags[8].item() == 3
     assert lib.b200_peer_handshake(flags.data_ptr(), peers, 9, 0, 0, 1, None) == N.E_BAD_ARG
     assert lib.b200_ep_dispatch(None, None, None, None, 4, 2, 2, 256, 8, 1, 0, peers, peers, peers, peers, None) == N.E_BAD_ARG
+
+
+def test_a_peer_that_never_signals_times_out_and_the_context_survives(monkeypatch):
+    """Failure detection without a fault: the "other rank" is a flag array that nothing writes. The
+    bounded wait gives up after the limit (100 ms here), the device status word reports it, reading
+    the word clears it, and the next launches on the same context work."""
+    import time
+
+    from sglang_b200 import _native as N
+
+    lib = N.load()
+    monkeypatch.setenv("B200_PEER_WAIT_MS", "100")
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    silent_peer = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peers = (ctypes.c_void_p * 2)(mine.data_ptr(), silent_peer.data_ptr())
+    assert N.read_device_status() == 0
+    t0 = time.time()
+    N.check(lib.b200_peer_handshake(mine.data_ptr(), peers, 2, 0, 0, 1, N.current_stream()), "handshake")
+    status = N.read_device_status()  # synchronises
+    waited = time.time() - t0
+    assert status == 2, "the expired wait must be reported"
+    assert 0.05 < waited < 1.5, waited
+    assert silent_peer[0].item() == 1  # our own signal did go out
+    assert N.read_device_status() == 0  # cleared by the read
+    # the all-reduce finishing kernel gives up the same way and leaves its output untouched
+    slot = torch.ones(2, 8, 256, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((8, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    outs = (ctypes.c_void_p * 1)(out.data_ptr())
+    N.check(lib.b200_allreduce_finish(slot.data_ptr(), 8 * 256, outs, N.BF16, 8, 256, 2, 0, 0, None, None, None, 1e-6,
+                                      mine.data_ptr(), peers, 5, None, None, N.current_stream()), "finish")
+    assert N.read_device_status() == 2 and torch.all(out == 7.0)
+    # the context is intact: a healthy single-rank call right after
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    self_only = (ctypes.c_void_p * 1)(flags.data_ptr())
+    N.check(lib.b200_allreduce_finish(slot.data_ptr(), 8 * 256, outs, N.BF16, 8, 256, 1, 0, 0, None, None, None, 1e-6,
+                                      flags.data_ptr(), self_only, 1, None, None, N.current_stream()), "finish")
+    assert N.read_device_status() == 0 and torch.all(out == 1.0)
