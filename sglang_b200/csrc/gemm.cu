@@ -20,6 +20,9 @@ template <typename OutT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ C,
                                                             int64_t mn, int splits, const FanOut fan, int64_t N) {
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  // launched with programmatic stream serialisation: this grid may start while the GEMM that
+  // writes the partials is still draining; everything above is index arithmetic only
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (i >= mn) return;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < splits; ++s) {
@@ -40,8 +43,24 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 template <typename OutT>
 static int launch_reduce(const float* partial, void* C, int64_t mn, int splits, cudaStream_t st,
                          const FanOut& fan = FanOut{}, int64_t N = 1) {
-  splitk_reduce_kernel<OutT><<<(unsigned)cdiv(mn, 8 * 256), 256, 0, st>>>(partial, static_cast<OutT*>(C), mn, splits,
-                                                                         fan, N);
+  // Programmatic dependent launch: the grid is set up while the producing GEMM finishes (the decode
+  // kernel signals launch_dependents once all its CTAs run); griddepcontrol.wait in the kernel holds
+  // it until the partials are complete and visible.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)cdiv(mn, 8 * 256));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<OutT>, partial, static_cast<OutT*>(C), mn, splits, fan, N);
+  if (e != cudaSuccess) {
+    set_error_detail("splitk_reduce_kernel: %s", cudaGetErrorString(e));
+    return B200_E_LAUNCH;
+  }
   return check_launch("splitk_reduce_kernel");
 }
 

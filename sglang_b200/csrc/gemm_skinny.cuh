@@ -87,7 +87,17 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
     ptx::prefetch_tensormap(&tmap_w);
     ptx::prefetch_tensormap(&tmap_x);
   }
-  // As[m, kb] * Bs[n0/128, kb] for this item's tokens and K blocks -> shared memory
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // every CTA of this grid is running: a dependent grid (the split-K reduction) may be set up now;
+  // it waits for this grid's completion before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The producer and the MMA issuer start at once; meanwhile the promotion warps stage
+  // As[m, kb] * Bs[n0/128, kb] for this item's tokens and K blocks in shared memory (their own
+  // 128-thread barrier: only they read the table), so the first weight tiles are already in
+  // flight while the scales are fetched.
   if (warp < 4) {
     const float* bs_row = p.Bs + (int64_t)nt * p.num_kb;
     for (int i = threadIdx.x; i < (kb1 - kb0) * NT; i += 128) {
@@ -95,11 +105,8 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
       const int m = m0 + t;
       scales[i] = m < p.M ? __ldg(p.As + (int64_t)m * p.as_sm + (int64_t)kb * p.as_sk) * __ldg(bs_row + kb) : 0.f;
     }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
   }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == kProducerWarp) {
     bool ok = true;
