@@ -99,6 +99,9 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
   // 128-thread barrier: only they read the table), so the first weight tiles are already in
   // flight while the scales are fetched.
   if (warp < 4) {
+    // the activation scales (and, at the end, the output buffer) belong to the kernels before this
+    // one in the stream: this grid is launched as their programmatic dependent, so wait for them here
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const float* bs_row = p.Bs + (int64_t)nt * p.num_kb;
     for (int i = threadIdx.x; i < (kb1 - kb0) * NT; i += 128) {
       const int kb = kb0 + i / NT, t = i % NT;
@@ -110,8 +113,21 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
 
   if (warp == kProducerWarp) {
     bool ok = true;
-    uint32_t it = 0;
-    for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+    // Prologue: the weights do not depend on the previous kernel, the quantised activations do.
+    // The weight tiles of the first stages are requested before waiting for that kernel, so the
+    // weight stream starts while it is still finishing.
+    const int npro = min(S, kb1 - kb0);
+    if (lane == 0) {
+      for (int i = 0; i < npro; ++i) {
+        ptx::mbar_expect_tx(full_bar(i), Cfg::kStageW + Cfg::kStageX);
+        ptx::tma_load_2d(sW + i * Cfg::kStageW, &tmap_w, (kb0 + i) * kBK, n0, full_bar(i));
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int i = 0; i < npro; ++i) ptx::tma_load_2d(sX + i * Cfg::kStageX, &tmap_x, (kb0 + i) * kBK, m0, full_bar(i));
+    }
+    __syncwarp();
+    uint32_t it = npro;
+    for (int kb = kb0 + npro; kb < kb1 && ok; ++kb, ++it) {
       const int s = it % S;
       ok = ptx::mbar_wait(empty_bar(s), ((it / S) & 1) ^ 1, abort_flag);
       if (!ok) break;
@@ -225,7 +241,23 @@ inline int launch_skinny_inst(const CUtensorMap& tw, const CUtensorMap& tx, cons
     return B200_E_LAUNCH;
   }
   const int grid = p.n_tiles * p.t_tiles * p.k_splits;
-  k<<<grid, SkinnyCfg<NT>::kThreads, smem, st>>>(tw, tx, p);
+  // programmatic dependent of the kernel before it (normally the activation quantiser, which
+  // signals launch_dependents at once): set-up and the first weight loads overlap its tail
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(SkinnyCfg<NT>::kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, k, tw, tx, p);
+  if (e != cudaSuccess) {
+    set_error_detail("block_fp8_gemm_skinny_kernel: %s", cudaGetErrorString(e));
+    return B200_E_LAUNCH;
+  }
   return check_launch("block_fp8_gemm_skinny_kernel");
 }
 

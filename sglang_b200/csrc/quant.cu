@@ -14,6 +14,9 @@ __global__ void __launch_bounds__(256) quant_group_kernel(const T* __restrict__ 
                                                           int64_t s_stride_g, float eps, int formula) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool active = c < total_chunks;  // whole lane-groups are active or not (total % LPG == 0)
+  // a GEMM launched as programmatic dependent may set itself up now; it waits for this grid's
+  // completion before it reads the bytes and scales written here
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   float f[16];
   if (active) {
     Vec16<T>::load(x + c * 16, f);
