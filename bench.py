@@ -213,6 +213,19 @@ def run_reference(args, rank: int):
     }))
 
 
+NVLINK_GBS = 770.0  # measured peer copy per direction per GPU on this pool (nominal 900)
+
+
+def roofline_frac(ms: float, flops: float, hbm_bytes: float = 0.0, link_bytes: float = 0.0) -> dict:
+    """Measured time against max(flops / FP8 peak, HBM bytes / copy rate, NVLink bytes / link rate), per GPU;
+    FP8 peak = 2 x the measured sustained dense bf16 rate."""
+    peaks = load_peaks()
+    terms = {"tensor": flops / (2 * peaks["bf16_sustained"] * 1e12), "hbm": hbm_bytes / (peaks["hbm_gbs"] * 1e9),
+             "nvlink": link_bytes / (NVLINK_GBS * 1e9)}
+    bound = max(terms, key=terms.get)
+    return {"roofline_frac": terms[bound] / (ms * 1e-3), "roofline_bound": bound}
+
+
 def bench_moe(S, device, steps: int):
     """Extra line items: fused-MoE tokens/s for the DeepSeek-V3 and Mixtral shaped layers (1 GPU)."""
     from sglang_b200 import synthetic
@@ -246,7 +259,10 @@ def bench_moe(S, device, steps: int):
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
+        active = int(torch.unique(ti).numel())
+        moe_bytes = 4 * T * H + 3 * H * I * active * (1 + 4 / 16384) + 8 * T * topk
         out[label] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "tflops": 6 * T * topk * H * I / ms / 1e9,
+                      **roofline_frac(ms, 6 * T * topk * H * I, moe_bytes),
                       "config": {"E": E, "topk": topk, "H": H, "I": I, "T": T, "weights_mb": (w1.numel() + w2.numel()) / 1e6}}
         del w1, w2, w1_s, w2_s
         torch.cuda.empty_cache()
@@ -314,9 +330,13 @@ def bench_parallel(S, device, rank: int, world: int, steps: int):
         for fused in (False, True):
             ms = timed(lambda: tp_step(rows, fused), steps)
             key = f"tp_llama70b_M{rows}" + ("_peer_fused" if fused else "")
+            # per GPU: 1/world of the flops, its weight shard streamed once, 2 all-reduces of [rows, 8192] bf16
+            w_bytes = sum(wq.numel() for _, _, wq, _ in layers)
             out[key] = {"tflops": flops * rows / M / ms / 1e9, "ms": ms, "tp": world,
                         "allreduce": "peer memory, fused with the GEMM" if fused else "nccl",
-                        "allreduce_bytes_per_step": 2 * rows * 8192 * 2}
+                        "allreduce_bytes_per_step": 2 * rows * 8192 * 2,
+                        **roofline_frac(ms, flops * rows / M / world, w_bytes,
+                                        2 * (world - 1) / world * 2 * rows * 8192 * 2)}
     del peer
     # the decode-sized step again, replayed from a CUDA graph (how a server runs decode): the peer
     # path uses device-side epochs and a single slot buffer so that the capture can be replayed
@@ -361,8 +381,16 @@ def bench_parallel(S, device, rank: int, world: int, steps: int):
             sl = slice(rank * per, (rank + 1) * per)
             xs, ws_, is_ = x[sl].contiguous(), tw[sl].contiguous(), ti[sl].contiguous()
         ms = timed(lambda: layer(xs, ws_, is_), max(2, steps // 2))
+        # per GPU: 1/world of the flops, its experts' weights once; all-to-all modes move every local token's
+        # FP8 row + scales to the other owning ranks and bf16 partial rows back (at most topk_group ranks per token)
+        per = T // world
+        link = 0.0 if mode == "ep" else per * min(cfg["topk_group"], world) * (world - 1) / world * (H + H // 32 + 2 * H)
+        if mode == "ep":
+            link = 2 * (world - 1) / world * T * H * 2
         out[f"ep_deepseek_v3_T16384_{label}"] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "ep": world,
-                                                 "tflops": 6 * T * topk * H * I / ms / 1e9}
+                                                 "tflops": 6 * T * topk * H * I / ms / 1e9,
+                                                 **roofline_frac(ms, 6 * T * topk * H * I / world,
+                                                                 3 * H * I * el * (1 + 4 / 16384), link)}
     return out
 
 
