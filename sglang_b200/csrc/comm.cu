@@ -107,7 +107,8 @@ __device__ void finish_epoch(uint32_t* my_flags, int phase, bool device_epoch) {
   }
 }
 
-template <typename T>
+// NR = number of ranks (compile time: the slot loop unrolls and all its loads are in flight together)
+template <typename T, int NR>
 __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReduceParams p) {
   __shared__ int s_ok;
   __shared__ float s_red[8];
@@ -125,28 +126,43 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
     return;
   }
   const int64_t N = p.N;
-  const T* slots = static_cast<const T*>(p.slots);
-  const T* residual = static_cast<const T*>(p.residual);
+  const T* __restrict__ slots = static_cast<const T*>(p.slots);
+  const T* residual = static_cast<const T*>(p.residual);  // may be the same buffer as residual_out (in place)
   const T* w = static_cast<const T*>(p.rms_weight);
   const int n_out = p.by_tile ? p.n_ranks : 1;
+  // fp32 sums of one 8-element chunk of a row: the slots in rank order, then the residual
+  auto sum_chunk = [&](int64_t row, int64_t c, float (&acc)[8]) {
+    uint4 raw[NR + 1];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+      raw[r] = __ldcg(reinterpret_cast<const uint4*>(slots + (int64_t)r * p.slot_stride + row * N + c));
+    raw[NR] = residual != nullptr ? *reinterpret_cast<const uint4*>(residual + row * N + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int r = 0; r <= NR; ++r) {  // rank order, then the residual (+0 when there is none)
+      const T* h = reinterpret_cast<const T*>(&raw[r]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+    }
+  };
+  auto store_out = [&](int64_t row, int64_t c, const uint4& o) {
+    if (p.out_mc != nullptr) multimem_st_16(static_cast<T*>(p.out_mc) + row * N + c, o);
+    else
+      for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+  };
+  // With a norm the row is needed twice (sum of squares, then the scaled values). The sums of the
+  // first kKeep chunks per thread (rows up to 8192 columns) stay in registers between the two
+  // passes; anything beyond is summed again from the slots.
+  constexpr int kKeep = 4;
+  const int64_t stride = (int64_t)blockDim.x * 8;
   for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
     if (p.by_tile && (row / 128) % p.n_ranks != p.rank) continue;
     float ss = 0.f;
-    // pass 1: sum (+ residual); with a norm the fp32 sums are parked in the first output
-    for (int64_t c = threadIdx.x * 8; c < N; c += blockDim.x * 8) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < p.n_ranks; ++r) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (int64_t)r * p.slot_stride + row * N + c));
-        const T* h = reinterpret_cast<const T*>(&v);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
-      }
-      if (residual != nullptr) {
-        const uint4 v = *reinterpret_cast<const uint4*>(residual + row * N + c);
-        const T* h = reinterpret_cast<const T*>(&v);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
-      }
+    float keep[kKeep][8];
+    // pass 1: sum (+ residual) -> residual_out, and -> out when there is no norm
+    auto pass1 = [&](int64_t c, float (&acc)[8]) {
+      sum_chunk(row, c, acc);
       uint4 o;
       T* oh = reinterpret_cast<T*>(&o);
 #pragma unroll
@@ -157,16 +173,23 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
           for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.residual_out[d]) + row * N + c) = o;
       }
       if (w == nullptr) {
-        if (p.out_mc != nullptr) multimem_st_16(static_cast<T*>(p.out_mc) + row * N + c, o);
-        else
-          for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+        store_out(row, c, o);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss += acc[i] * acc[i];
       }
+    };
+#pragma unroll
+    for (int it = 0; it < kKeep; ++it) {
+      const int64_t c = threadIdx.x * 8 + it * stride;
+      if (c < N) pass1(c, keep[it]);
+    }
+    for (int64_t c = threadIdx.x * 8 + kKeep * stride; c < N; c += stride) {
+      float acc[8];
+      pass1(c, acc);
     }
     if (w != nullptr) {
-      // RMSNorm over the row from the unrounded fp32 sums (recomputed: the row is hot in L1/L2)
+      // RMSNorm over the row from the unrounded fp32 sums
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
@@ -175,30 +198,24 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
       for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += s_red[i];
       const float inv = rsqrtf(tot / (float)N + p.eps);
       __syncthreads();
-      for (int64_t c = threadIdx.x * 8; c < N; c += blockDim.x * 8) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < p.n_ranks; ++r) {
-          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (int64_t)r * p.slot_stride + row * N + c));
-          const T* h = reinterpret_cast<const T*>(&v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
-        }
-        if (residual != nullptr) {
-          // residual_out may alias residual: read what pass 1 stored only if it did not alias
-          const uint4 v = *reinterpret_cast<const uint4*>(residual + row * N + c);
-          const T* h = reinterpret_cast<const T*>(&v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
-        }
+      auto pass2 = [&](int64_t c, const float (&acc)[8]) {
         const uint4 wv = *reinterpret_cast<const uint4*>(w + c);
         const T* wh = reinterpret_cast<const T*>(&wv);
         uint4 o;
         T* oh = reinterpret_cast<T*>(&o);
 #pragma unroll
         for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * inv * to_f32<T>(wh[i]));
-        if (p.out_mc != nullptr) multimem_st_16(static_cast<T*>(p.out_mc) + row * N + c, o);
-        else
-          for (int d = 0; d < n_out; ++d) *reinterpret_cast<uint4*>(static_cast<T*>(p.out[d]) + row * N + c) = o;
+        store_out(row, c, o);
+      };
+#pragma unroll
+      for (int it = 0; it < kKeep; ++it) {
+        const int64_t c = threadIdx.x * 8 + it * stride;
+        if (c < N) pass2(c, keep[it]);
+      }
+      for (int64_t c = threadIdx.x * 8 + kKeep * stride; c < N; c += stride) {
+        float acc[8];
+        sum_chunk(row, c, acc);  // residual_out never aliases residual when a norm is asked for
+        pass2(c, acc);
       }
     }
   }
@@ -271,8 +288,16 @@ extern "C" int b200_allreduce_finish(const void* slots, int64_t slot_stride, voi
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int64_t want = M < (int64_t)sms * 8 ? M : (int64_t)sms * 8;
-  if (dtype == B200_BF16) allreduce_finish_kernel<__nv_bfloat16><<<(unsigned)want, 256, 0, st>>>(p);
-  else allreduce_finish_kernel<__half><<<(unsigned)want, 256, 0, st>>>(p);
+#define B200_FINISH(NR)                                                                           \
+  case NR:                                                                                        \
+    if (dtype == B200_BF16) allreduce_finish_kernel<__nv_bfloat16, NR><<<(unsigned)want, 256, 0, st>>>(p); \
+    else allreduce_finish_kernel<__half, NR><<<(unsigned)want, 256, 0, st>>>(p);                  \
+    break;
+  switch (n_ranks) {
+    B200_FINISH(1) B200_FINISH(2) B200_FINISH(3) B200_FINISH(4) B200_FINISH(5) B200_FINISH(6) B200_FINISH(7) B200_FINISH(8)
+    default: break;
+  }
+#undef B200_FINISH
   int rc = check_launch("allreduce_finish_kernel");
   if (rc || !p.by_tile) return rc;
   allreduce_results_landed_kernel<<<1, 32, 0, st>>>(p);
