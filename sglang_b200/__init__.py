@@ -30,3 +30,4 @@ from .topk import (  # noqa: F401,E402
     topk_softmax,
 )
 from . import fp8  # noqa: F401,E402
+from . import custom_ops  # noqa: F401,E402  (registers torch.ops.sglang_b200.*)
