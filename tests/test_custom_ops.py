@@ -143,3 +143,33 @@ def test_moe_ops_equal_direct_calls():
     xin = x.clone()
     ops.inplace_fused_experts(xin, w1, w2, tw, ti, s1, s2, [128, 128], False, None)
     assert torch.equal(xin, ref)
+
+
+@pytest.mark.gpu
+def test_ops_trace_and_capture():
+    """A quantised linear written with the dispatcher ops traces as one graph (no graph break: the fake
+    implementations supply the shapes) and captures into a CUDA graph; both replay the eager bits."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    M, K, Nn = 48, 1024, 768
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(Nn, K, device="cuda", generator=g) * 0.5).to(fp8)
+    ws = torch.rand(Nn // 128, K // 128, device="cuda", generator=g)
+
+    def linear(x):
+        q = torch.empty_like(x, dtype=fp8)
+        s = torch.empty(K // 128, x.shape[0], device=x.device).t()
+        ops.sgl_per_token_group_quant_8bit(x, q, s, 128, 1e-10, -448.0, 448.0, False)
+        return ops.fp8_blockwise_scaled_mm(q, w.t(), s, ws.t(), torch.bfloat16)
+
+    eager = linear(x)
+    traced = torch.compile(linear, backend="eager", fullgraph=True)
+    assert torch.equal(traced(x), eager)
+    linear(x)  # workspaces exist before capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = linear(x)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
