@@ -193,8 +193,17 @@ def run_reference(args, rank: int):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    rows = 64
-    acts, weights = cpu_inputs(rows)
+    acts, weights = cpu_inputs(2048)
+    # Size the step from one probe pass: about 1.5 s of host work per step (less when many steps are asked
+    # for, so that the whole run stays near two minutes), at least 64 rows. Larger samples amortise the
+    # per-call weight dequantisation the way the full 8192-row workload does.
+    cpu_linears(64, threads, weights, acts)
+    cpu_linears(256, threads, weights, acts)
+    t1 = time.perf_counter()
+    cpu_linears(256, threads, weights, acts)
+    per_256 = time.perf_counter() - t1
+    target = min(1.5, 120.0 / max(1, args.steps + args.warmup))
+    rows = int(max(64, min(2048, 256 * target / max(per_256, 1e-3)))) // 32 * 32
     for _ in range(args.warmup):
         cpu_linears(rows, threads, weights, acts)
     t0 = time.perf_counter()
