@@ -235,6 +235,75 @@ def roofline_frac(ms: float, flops: float, hbm_bytes: float = 0.0, link_bytes: f
     return {"roofline_frac": terms[bound] / (ms * 1e-3), "roofline_bound": bound}
 
 
+def graph_time_us(fns, rounds: int = 5) -> float:
+    """Device time per call, in microseconds: the calls of ``fns`` captured once into a CUDA graph (no host
+    launch gaps), median of ``rounds`` replays timed with events on the replaying stream."""
+    for fn in fns[:3]:
+        fn()
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fns[0]()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for fn in fns:
+                fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(rounds):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / len(fns))
+    return sorted(times)[len(times) // 2]
+
+
+def bench_kernels(S, device):
+    """Extra line items for the HBM-bound kernels of the path: achieved GB/s on algorithmic bytes and the fraction
+    of the measured copy rate. Inputs exceed L2, or (decode linears) every call of a replay reads another copy of
+    the weight so that weights come from HBM as they do in a model with many layers."""
+    from sglang_b200.topk import biased_grouped_topk
+
+    hbm = load_peaks()["hbm_gbs"]
+    g = torch.Generator(device=device).manual_seed(77)
+    fp8 = torch.float8_e4m3fn
+    out = {}
+
+    def item(us, nbytes, **extra):
+        gbs = nbytes / us / 1e3
+        return {"us": us, "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, **extra}
+
+    M, K = 8192, 14336
+    x = torch.randn(M, K, device=device, generator=g).bfloat16()
+    us = graph_time_us([lambda: S.per_token_group_quant_fp8(x, 128, column_major_scales=True)] * 4)
+    out["per_token_group_quant_fp8_8192x14336_bf16"] = item(us, M * K * 3 + M * (K // 128) * 4)
+    del x
+    T, E, topk = 16384, 256, 8
+    logits = torch.randn(T, E, device=device, generator=g)
+    bias = torch.zeros(E, device=device)
+    us = graph_time_us([lambda: biased_grouped_topk(logits, logits, bias, topk, True, 8, 4)] * 4)
+    out["biased_grouped_topk_16384x256_top8"] = item(us, T * E * 4 + T * topk * 8)
+    _, ids = biased_grouped_topk(logits, logits, bias, topk, True, 8, 4)
+    us = graph_time_us([lambda: S.moe_align_block_size(ids, 128, E)] * 4)
+    max_pad = T * topk + (E + 1) * 127
+    out["moe_align_block_size_16384x8_E256"] = item(us, T * topk * 4 + 4 * (max_pad + max_pad // 128 + E + 3))
+    for name, n, k in LINEARS:
+        copies = max(3, -(-400_000_000 // (n * k)))
+        ws = [torch.randn(n, k, device=device, generator=g).to(fp8) for _ in range(copies)]
+        wscale = torch.rand(n // 128, k // 128, device=device, generator=g)
+        for m in (1, 16):
+            xm = torch.randn(m, k, device=device, generator=g).bfloat16()
+            fns = [(lambda w=w: S.w8a8_block_fp8_linear(xm, w, [128, 128], wscale)) for w in ws]
+            us = graph_time_us(fns)
+            out[f"linear_{name}_M{m}"] = item(us, n * k + n * k // 16384 * 4 + m * k * 2 + m * n * 2, N=n, K=k,
+                                              weight_copies_rotated=copies)
+        del ws
+    torch.cuda.empty_cache()
+    return out
+
+
 def bench_moe(S, device, steps: int):
     """Extra line items: fused-MoE tokens/s for the DeepSeek-V3 and Mixtral shaped layers (1 GPU)."""
     from sglang_b200 import synthetic
@@ -552,6 +621,10 @@ def main():
             except Exception as e:  # the headline number stands without the extra line items
                 line["moe"] = {"error": repr(e)}
         if world == 1:
+            try:
+                line["kernels"] = bench_kernels(S, device)
+            except Exception as e:  # the headline number stands without the extra line items
+                line["kernels"] = {"error": repr(e)}
             line["cpu_baseline"] = time_cpu_baseline()
     if rank == 0:
         print(json.dumps(line))

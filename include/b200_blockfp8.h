@@ -39,8 +39,12 @@ enum { B200_BF16 = 0, B200_F16 = 1, B200_F32 = 2, B200_I32 = 3, B200_I64 = 4 };
 /* quant arithmetic variants (all: amax = max(|x|, eps) over the group, fp32)
  *   0: s = amax / 448,     q = x / s        (reference torch-native + CUDA v1)
  *   1: s = amax / 448,     q = x * (1 / s)  (reference Triton row-major)
- *   2: s = amax * (1/448), q = x * (448 / amax)  (reference CUDA v2)                    */
-enum { B200_QUANT_DIV = 0, B200_QUANT_RECIP = 1, B200_QUANT_V2 = 2 };
+ *   2: s = amax * (1/448), q = x * (448 / amax)  (reference CUDA v2)
+ *   3: variant 0 computed without a per-element division: r = 1/s correctly rounded,
+ *      q0 = x * r, q = copysign(fma(fma(-q0, s, x), r, q0), x). For bf16 and f16 inputs with eps = 1e-10 the
+ *      bytes and scales equal variant 0's for every (x, amax) pair that exists (both types have
+ *      fewer than 2^31 such pairs; the GPU tests enumerate them all). Not claimed for f32 input. */
+enum { B200_QUANT_DIV = 0, B200_QUANT_RECIP = 1, B200_QUANT_V2 = 2, B200_QUANT_DIV_CORRECTED = 3 };
 
 const char* b200_status_string(int status);
 const char* b200_last_error_detail(void);

@@ -152,6 +152,15 @@ __device__ __forceinline__ float quant16(const float (&f)[16], float amax, int f
     float r = __fdiv_rn(1.0f, s);
 #pragma unroll
     for (int i = 0; i < 16; ++i) q[i] = f[i] * r;
+  } else if (formula == B200_QUANT_DIV_CORRECTED) {
+    s = __fdiv_rn(amax, 448.0f);
+    const float r = __frcp_rn(s);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float q0 = f[i] * r;
+      // one residual step towards the rounded quotient; a zero result takes the sign of x as x / s does
+      q[i] = copysignf(fmaf(fmaf(-q0, s, f[i]), r, q0), f[i]);
+    }
   } else {
     s = __fdiv_rn(amax, 448.0f);
 #pragma unroll

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float q0 = f[i] * inv;
-      f[i] = fmaf(fmaf(-q0, scale, f[i]), inv, q0);
+      f[i] = copysignf(fmaf(fmaf(-q0, scale, f[i]), inv, q0), f[i]);  // -0 stays -0, as with x / scale
     }
     uint4 out;
     out.x = pack4_e4m3(f[0], f[1], f[2], f[3]);
@@ -278,7 +278,7 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
       uint8_t* xq = ws + L.off_xq;
       float* xs = reinterpret_cast<float*>(ws + L.off_xs);
       rc = b200_per_token_group_quant_fp8(hidden, std::is_same<T, __half>::value ? B200_F16 : B200_BF16, xq, xs, T_tokens,
-                                          H, 128, H / 128, 1, 1e-10f, B200_QUANT_DIV, st);
+                                          H, 128, H / 128, 1, 1e-10f, B200_QUANT_DIV_CORRECTED, st);  // 16-bit input: same bits as the division
       if (rc) return rc;
       hq = xq;
       hs = xs;

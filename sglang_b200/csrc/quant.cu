@@ -210,7 +210,7 @@ extern "C" int b200_per_token_group_quant_fp8(const void* x, int x_dtype, void* 
   if (M == 0 || K == 0) return B200_OK;
   B200_CHECK_ARG(x && q && s, "quant: null pointer");
   B200_CHECK_ARG(group > 0 && K % group == 0, "quant: K=%lld is not a multiple of group=%d", (long long)K, group);
-  B200_CHECK_ARG(formula >= 0 && formula <= 2, "quant: unknown formula %d", formula);
+  B200_CHECK_ARG(formula >= 0 && formula <= 3, "quant: unknown formula %d", formula);
   B200_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)q & 15) == 0, "quant: x and q must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (x_dtype) {

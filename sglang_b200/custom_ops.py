@@ -108,7 +108,7 @@ def _quant_into(x, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_
     with N.on_device(x):
         st = lib.b200_per_token_group_quant_fp8(
             N.ptr(x), N.DTYPE_CODE[x.dtype], N.ptr(output_q), N.ptr(output_s), rows, k, group_size,
-            output_s.stride(0), output_s.stride(1), eps, _q._QUANT_FORMULA, N.current_stream())
+            output_s.stride(0), output_s.stride(1), eps, _q.quant_formula_for(x.dtype, eps), N.current_stream())
     N.check(st, "sgl_per_token_group_quant_8bit")
 
 

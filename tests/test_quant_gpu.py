@@ -91,3 +91,49 @@ def test_empty_and_errors():
         S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16, device="cuda"), 128, fuse_silu_and_mul=True)
     with pytest.raises(RuntimeError):
         S.per_token_group_quant_fp8(torch.zeros(2, 256, dtype=torch.bfloat16), 128)
+
+
+@pytest.mark.parametrize("dtype,max_pattern", [(torch.bfloat16, 0x7F7F), (torch.float16, 0x7BFF)])
+def test_corrected_reciprocal_equals_division_for_every_16bit_pair(dtype, max_pattern):
+    """Arithmetic variant 3 (reciprocal + one residual step) against variant 0 (IEEE division) on EVERY
+    pair (x, amax) a 16-bit input can produce: for each positive finite bit pattern ``a`` taken as the group's
+    amax, every value of magnitude <= a with either sign appears in some group whose first element is ``a``.
+    Bytes and scales must be identical; this is what allows the wrapper to use variant 3 for 16-bit inputs."""
+    from sglang_b200 import _native as N
+
+    lib = N.load()
+    code = N.DTYPE_CODE[dtype]
+    dev = torch.device("cuda")
+    slots = torch.arange(127, device=dev, dtype=torch.int64)[None, :]
+    pairs = 0
+    step = 2048
+    for i0 in range(0, max_pattern + 1, step):
+        i_vals = torch.arange(i0, min(i0 + step, max_pattern + 1), device=dev, dtype=torch.int64)
+        n_groups = (2 * (i_vals + 1) + 126) // 127
+        amax_of_group = torch.repeat_interleave(i_vals, n_groups)
+        first = torch.cumsum(n_groups, 0) - n_groups
+        local = torch.arange(amax_of_group.numel(), device=dev, dtype=torch.int64) - torch.repeat_interleave(first, n_groups)
+        e = local[:, None] * 127 + slots
+        cnt = (amax_of_group + 1)[:, None]
+        pattern = torch.where(e < cnt, e, torch.where(e < 2 * cnt, 0x8000 | (e - cnt), torch.zeros_like(e)))
+        rows = torch.cat([amax_of_group[:, None], pattern], 1)
+        del e, pattern
+        x = torch.where(rows >= 0x8000, rows - 0x10000, rows).to(torch.int16).view(dtype).contiguous()
+        del rows
+        M = x.shape[0]
+        pairs += int((2 * (i_vals + 1)).sum())
+        outs = []
+        for formula in (0, 3):
+            q = torch.empty(M, 128, dtype=torch.uint8, device=dev)
+            s = torch.empty(M, dtype=torch.float32, device=dev)
+            st = lib.b200_per_token_group_quant_fp8(N.ptr(x), code, N.ptr(q), N.ptr(s), M, 128, 128, 1, 1, 1e-10, formula,
+                                                    N.current_stream())
+            N.check(st, "per_token_group_quant_fp8")
+            outs.append((q, s))
+        assert torch.equal(outs[0][1], outs[1][1])
+        same = outs[0][0] == outs[1][0]
+        if not bool(same.all()):
+            bad = (~same).nonzero()[:5]
+            raise AssertionError(f"bytes differ, first (row, col): {bad.tolist()}, amax patterns from {i0}")
+        del x, outs
+    assert pairs == (max_pattern + 1) * (max_pattern + 2)  # 2 * sum_{i=0..max} (i + 1)
