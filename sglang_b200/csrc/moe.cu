@@ -57,8 +57,9 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(
     amax = fmaxf(group_max<8>(amax), 1e-10f);
     // scale = amax / 448 and q = x / scale as the reference's quantiser computes them. The quotient
     // is formed as x * (1 / scale) plus one residual correction (rem = x - q * scale, exact in an
-    // FMA): two FMAs per element instead of an IEEE division sequence, and the same fp32 value
-    // as the division except for quotients within 2^-23 ulp of a rounding boundary. A plain
+    // FMA): two FMAs per element instead of an IEEE division sequence. For 16-bit inputs the
+    // FP8 bytes equal those of the division on every (x, amax) pair (the quantiser's tests
+    // enumerate them all). A plain
     // reciprocal multiply is not enough for 16-bit inputs: when amax has a short mantissa many
     // quotients sit exactly on an FP8 tie and would be broken the other way.
     const float scale = __fdiv_rn(amax, 448.0f);
