@@ -210,6 +210,17 @@ int b200_route_topk(const void* logits, int logits_dtype, const float* correctio
                     int renormalize, float output_scale, const int32_t* num_token_non_padded,
                     float* topk_weights, int32_t* topk_ids, void* stream);
 
+/* Softmax top-k over transformed logits
+ * replaces: torch.ops.sgl_kernel.topk_softmax with moe_softcapping and / or correction_bias
+ *           (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:85-115, 428-458, 720-816)
+ * v = logits; softcap != 0: v = tanh(v / softcap) * softcap; logit_bias (fp32 [E], may be NULL): v += bias;
+ * scores = softmax(v) per row; top-k of the scores (ties to the lower index), weights = those scores,
+ * divided by their sum when renormalize != 0. Unlike b200_route_topk's correction_bias, which only
+ * steers the selection, this bias is part of the scores. Same limits, no workspace. */
+int b200_route_topk_softmax_capped(const void* logits, int logits_dtype, float softcap,
+                                   const float* logit_bias, int64_t T, int E, int topk, int renormalize,
+                                   float* topk_weights, int32_t* topk_ids, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Row-parallel linear with the tensor-parallel all-reduce done over peer memory
  * replaces: python/sglang/srt/layers/linear.py:1543-1558 (RowParallelLinear.forward: GEMM, then

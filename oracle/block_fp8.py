@@ -59,6 +59,7 @@ __all__ = [
     "pack_ue8m0_mn_major",
     "per_token_group_quant_fp8_ue8m0",
     "softmax_topk",
+    "softmax_topk_capped",
     "biased_grouped_topk",
     "sigmoid_topk",
     "grouped_topk",
@@ -464,3 +465,23 @@ def rel_frobenius(x: torch.Tensor, ref: torch.Tensor) -> float:
     x = x.to(torch.float64)
     ref = ref.to(torch.float64)
     return float((x - ref).norm() / ref.norm().clamp(min=1e-30))
+
+
+def softmax_topk_capped(logits: torch.Tensor, topk: int, renormalize: bool, softcap: float = 0.0,
+                        logit_bias: torch.Tensor = None):
+    """Softmax top-k over transformed logits, the arithmetic of the reference's ``topk_softmax`` kernel with
+    ``moe_softcapping`` / ``correction_bias`` (sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:101-130):
+    ``v = tanh(x / cap) * cap`` when ``cap != 0``, ``v += bias``, ``scores = softmax(v)``, top-k of the scores
+    (lower index wins ties), weights optionally divided by their sum. fp32 throughout. Parity unpinned: the
+    reference's tests (sgl-kernel/tests/test_moe_topk_softmax.py) never pass these two arguments, so this follows
+    the kernel text only; with both arguments off it equals ``softmax_topk``, which is pinned."""
+    v = logits.float()
+    if softcap != 0.0:
+        v = torch.tanh(v / torch.tensor(softcap, dtype=torch.float32)) * torch.tensor(softcap, dtype=torch.float32)
+    if logit_bias is not None:
+        v = v + logit_bias.float().unsqueeze(0)
+    scores = torch.softmax(v, dim=-1)
+    w, ids = _topk(scores, topk)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids.to(torch.int32)

@@ -84,6 +84,10 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
          c_void_p, c_void_p, c_void_p],
     ),
+    "b200_route_topk_softmax_capped": (
+        c_int,
+        [c_void_p, c_int, c_float, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ),
 }
 
 BF16, F16, F32, I32, I64 = 0, 1, 2, 3, 4

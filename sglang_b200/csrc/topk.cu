@@ -30,6 +30,8 @@ struct RouteParams {
   int group_top2;               // group score: 1 = sum of the two largest, 0 = maximum
   int renormalize;
   float out_scale;              // multiplies the weights after renormalisation (1 = none)
+  float softcap;                // != 0: logits become tanh(x / softcap) * softcap before scoring
+  const float* logit_bias;      // [E] or nullptr: added to the (soft-capped) logits before scoring
 };
 
 constexpr float kNegInf = -__builtin_huge_valf();
@@ -63,6 +65,17 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
   for (int j = 0; j < VMAX; ++j) {
     const bool valid = j < vpl && e0 + j < E;
     s[j] = valid ? to_f32<T>(row[e0 + j]) : kNegInf;
+  }
+  if (p.softcap != 0.f || p.logit_bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < VMAX; ++j) {
+      if (j < vpl && e0 + j < E) {
+        float v = s[j];
+        if (p.softcap != 0.f) v = tanhf(v / p.softcap) * p.softcap;
+        if (p.logit_bias != nullptr) v += __ldg(p.logit_bias + e0 + j);
+        s[j] = v;
+      }
+    }
   }
   if (p.sigmoid) {
 #pragma unroll
@@ -204,6 +217,15 @@ static int launch_route(const RouteParams& p, cudaStream_t st) {
   return check_launch("route_topk_kernel");
 }
 
+static int launch_route_dtype(const RouteParams& p, int logits_dtype, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (logits_dtype == B200_F32) return launch_route<float>(p, st);
+  if (logits_dtype == B200_BF16) return launch_route<__nv_bfloat16>(p, st);
+  if (logits_dtype == B200_F16) return launch_route<__half>(p, st);
+  set_error_detail("route_topk: logits dtype code %d is not f32/bf16/f16", logits_dtype);
+  return B200_E_UNSUPPORTED;
+}
+
 }  // namespace b200
 
 extern "C" int b200_route_topk(const void* logits, int logits_dtype, const float* correction_bias, int64_t T, int E,
@@ -231,10 +253,21 @@ extern "C" int b200_route_topk(const void* logits, int logits_dtype, const float
   p.weights = topk_weights; p.ids = topk_ids; p.T = T; p.E = E; p.vpl = (E + 31) / 32; p.topk = topk;
   p.sigmoid = scoring == B200_SCORE_SIGMOID; p.n_group = n_group; p.topk_group = topk_group;
   p.group_top2 = group_score == B200_GROUP_TOP2_SUM; p.renormalize = renormalize; p.out_scale = output_scale;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (logits_dtype == B200_F32) return launch_route<float>(p, st);
-  if (logits_dtype == B200_BF16) return launch_route<__nv_bfloat16>(p, st);
-  if (logits_dtype == B200_F16) return launch_route<__half>(p, st);
-  set_error_detail("route_topk: logits dtype code %d is not f32/bf16/f16", logits_dtype);
-  return B200_E_UNSUPPORTED;
+  return b200::launch_route_dtype(p, logits_dtype, stream);
+}
+
+extern "C" int b200_route_topk_softmax_capped(const void* logits, int logits_dtype, float softcap, const float* logit_bias,
+                                              int64_t T, int E, int topk, int renormalize, float* topk_weights,
+                                              int32_t* topk_ids, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(T >= 0 && E > 0 && topk > 0, "route_topk: bad shape T=%lld E=%d topk=%d", (long long)T, E, topk);
+  if (T == 0) return B200_OK;
+  B200_CHECK_ARG(logits && topk_weights && topk_ids, "route_topk: null pointer");
+  B200_CHECK_ARG(topk <= E, "route_topk: topk=%d > E=%d", topk, E);
+  B200_CHECK_ARG(softcap >= 0.f, "route_topk: negative softcap");
+  B200_UNSUPPORTED(E > 1024 || topk > 32, "route_topk: E=%d > 1024 or topk=%d > 32", E, topk);
+  RouteParams p = {};
+  p.logits = logits; p.weights = topk_weights; p.ids = topk_ids; p.T = T; p.E = E; p.vpl = (E + 31) / 32; p.topk = topk;
+  p.renormalize = renormalize; p.out_scale = 1.0f; p.softcap = softcap; p.logit_bias = logit_bias;
+  return launch_route_dtype(p, logits_dtype, stream);
 }

@@ -186,9 +186,7 @@ def _align_fake(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids
 
 @_impl("topk_softmax")
 def _topk_softmax(topk_weights, topk_indices, gating_output, renormalize, moe_softcapping, correction_bias):
-    if moe_softcapping != 0.0 or correction_bias is not None:
-        raise NotImplementedError("soft-capping and a softmax correction bias are not part of this path")
-    _topk.topk_softmax(topk_weights, topk_indices, gating_output, renormalize)
+    _topk.topk_softmax(topk_weights, topk_indices, gating_output, renormalize, moe_softcapping, correction_bias)
 
 
 @_fake("topk_softmax")

@@ -76,10 +76,42 @@ def _scoring_code(scoring_func: str) -> int:
 
 # ------------------------------------------------------------- sgl-kernel style (in place)
 def topk_softmax(
-    topk_weights: torch.Tensor, topk_ids: torch.Tensor, gating_output: torch.Tensor, renormalize: bool = False
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    gating_output: torch.Tensor,
+    renormalize: bool = False,
+    moe_softcapping: float = 0.0,
+    correction_bias: Optional[torch.Tensor] = None,
 ) -> None:
-    """sgl-kernel ``topk_softmax`` (sgl-kernel/python/sgl_kernel/moe.py): fills the two outputs."""
-    _route(gating_output, topk_ids.shape[1], renormalize, SOFTMAX, topk_weights=topk_weights, topk_ids=topk_ids)
+    """sgl-kernel ``topk_softmax`` (sgl-kernel/python/sgl_kernel/moe.py:28-54): fills the two outputs.
+    ``moe_softcapping != 0`` turns the logits into ``tanh(x / cap) * cap`` and ``correction_bias`` (fp32
+    ``[num_experts]``) is added to them, both BEFORE the softmax, as the reference kernel does
+    (moe_topk_softmax_kernels.cu:107-115)."""
+    if moe_softcapping == 0.0 and correction_bias is None:
+        _route(gating_output, topk_ids.shape[1], renormalize, SOFTMAX, topk_weights=topk_weights, topk_ids=topk_ids)
+        return
+    assert gating_output.dim() == 2, "gating_output must be [num_tokens, num_experts]"
+    N.require_cuda(gating_output, topk_weights, topk_ids)
+    assert gating_output.dtype in (torch.float32, torch.bfloat16, torch.float16), "unsupported logits dtype"
+    logits = gating_output if gating_output.is_contiguous() else gating_output.contiguous()
+    T, E = logits.shape
+    topk = topk_ids.shape[1]
+    assert topk_weights.dtype == torch.float32 and topk_ids.dtype == torch.int32
+    assert topk_weights.is_contiguous() and topk_ids.is_contiguous()
+    assert tuple(topk_weights.shape) == (T, topk) and tuple(topk_ids.shape) == (T, topk)
+    if correction_bias is not None:
+        assert correction_bias.dim() == 1 and correction_bias.shape[0] == E, "correction_bias size must match num_experts"
+        assert correction_bias.dtype == torch.float32, "correction_bias must be float32"
+        N.require_cuda(correction_bias)
+        correction_bias = correction_bias.contiguous()
+    if T == 0:
+        return
+    with N.on_device(logits):
+        st = N.load().b200_route_topk_softmax_capped(
+            N.ptr(logits), N.DTYPE_CODE[logits.dtype], float(moe_softcapping), N.ptr(correction_bias), T, E, topk,
+            int(bool(renormalize)), N.ptr(topk_weights), N.ptr(topk_ids), N.current_stream(),
+        )
+    N.check(st, "route_topk_softmax_capped")
 
 
 def topk_sigmoid(

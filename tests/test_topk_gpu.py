@@ -152,3 +152,35 @@ def test_routing_feeds_fused_experts_under_graph_capture():
     gr.replay()
     torch.cuda.synchronize()
     _same(w, ids, *O.biased_grouped_topk(logits, torch.zeros(256), 8, 8, 4, True))
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (37, 64, 6), (256, 128, 8), (19, 200, 4)])
+@pytest.mark.parametrize("cap,with_bias", [(30.0, False), (0.0, True), (5.0, True)])
+def test_softmax_with_softcapping_and_bias(T, E, k, cap, with_bias):
+    """``topk_softmax(..., moe_softcapping, correction_bias)``: both act on the logits before the softmax.
+    Weights to rtol 1e-5 (tanh and exp of the device library against the host's); ids exact except where two
+    scores are closer than that tolerance, which the comparison of weight-sorted values covers."""
+    from sglang_b200 import topk as R
+
+    g = torch.Generator().manual_seed(100 * T + E + k)
+    x = torch.randn(T, E, generator=g) * 4
+    bias = torch.randn(E, generator=g) * 0.5 if with_bias else None
+    w = torch.empty(T, k, device="cuda")
+    ids = torch.empty(T, k, dtype=torch.int32, device="cuda")
+    for renorm in (False, True):
+        R.topk_softmax(w, ids, x.cuda(), renorm, cap, bias.cuda() if with_bias else None)
+        ref_w, ref_ids = O.softmax_topk_capped(x, k, renorm, cap, bias)
+        torch.testing.assert_close(w.cpu(), ref_w, rtol=1e-5, atol=1e-8)
+        same = ids.cpu() == ref_ids
+        if not bool(same.all()):  # a swap is only acceptable between scores equal within the tolerance
+            torch.testing.assert_close(w.cpu()[~same], ref_w[~same], rtol=1e-5, atol=1e-8)
+            assert torch.equal(torch.sort(ids.cpu(), dim=1).values, torch.sort(ref_ids, dim=1).values)
+    # the dispatcher op takes the same arguments
+    w2 = torch.empty_like(w)
+    ids2 = torch.empty_like(ids)
+    torch.ops.sglang_b200.topk_softmax(w2, ids2, x.cuda(), True, cap, bias.cuda() if with_bias else None)
+    assert torch.equal(w2, w) and torch.equal(ids2, ids)
+    # off switches fall back to the plain kernel's result
+    R.topk_softmax(w, ids, x.cuda(), True, 0.0, None)
+    pw, pids = R.fused_topk(x.cuda(), x.cuda(), k, True)
+    assert torch.equal(w, pw) and torch.equal(ids, pids)
