@@ -7,11 +7,11 @@
 
 namespace b200 {
 
-template <typename T, int LPG>
+template <typename T, int LPG, int FORMULA>
 __global__ void __launch_bounds__(256) quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ q,
                                                           float* __restrict__ s, int64_t total_chunks,
                                                           int chunks_per_row, int64_t s_stride_m,
-                                                          int64_t s_stride_g, float eps, int formula) {
+                                                          int64_t s_stride_g, float eps) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool active = c < total_chunks;  // whole lane-groups are active or not (total % LPG == 0)
   // a GEMM launched as programmatic dependent may set itself up now; it waits for this grid's
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) quant_group_kernel(const T* __restrict__ 
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
   amax = fmaxf(group_max<LPG>(amax), eps);
   uint4 out;
-  const float scale = quant16(f, amax, formula, out);
+  const float scale = quant16(f, amax, FORMULA, out);
   if (active) {
     *reinterpret_cast<uint4*>(q + c * 16) = out;
     if ((threadIdx.x & (LPG - 1)) == 0) {
@@ -52,10 +52,17 @@ static int launch_quant(const void* x, void* q, float* s, int64_t M, int64_t K, 
     return B200_E_UNSUPPORTED;
   }
   const int cpr = (int)(K / 16);
-#define B200_Q_LAUNCH(LPG)                                                                              \
-  quant_group_kernel<T, LPG><<<(unsigned)blocks, threads, 0, st>>>(static_cast<const T*>(x),            \
-                                                                   static_cast<uint8_t*>(q), s, total, \
-                                                                   cpr, ssm, ssg, eps, formula)
+#define B200_Q_LAUNCH_F(LPG, F)                                                                            \
+  quant_group_kernel<T, LPG, F><<<(unsigned)blocks, threads, 0, st>>>(static_cast<const T*>(x),            \
+                                                                      static_cast<uint8_t*>(q), s, total, \
+                                                                      cpr, ssm, ssg, eps)
+#define B200_Q_LAUNCH(LPG)                                        \
+  switch (formula) {                                              \
+    case B200_QUANT_RECIP: B200_Q_LAUNCH_F(LPG, B200_QUANT_RECIP); break; \
+    case B200_QUANT_V2: B200_Q_LAUNCH_F(LPG, B200_QUANT_V2); break;       \
+    case B200_QUANT_DIV_CORRECTED: B200_Q_LAUNCH_F(LPG, B200_QUANT_DIV_CORRECTED); break; \
+    default: B200_Q_LAUNCH_F(LPG, B200_QUANT_DIV); break;         \
+  }
   switch (group) {
     case 16: B200_Q_LAUNCH(1); break;
     case 32: B200_Q_LAUNCH(2); break;
@@ -68,6 +75,7 @@ static int launch_quant(const void* x, void* q, float* s, int64_t M, int64_t K, 
       return B200_E_UNSUPPORTED;
   }
 #undef B200_Q_LAUNCH
+#undef B200_Q_LAUNCH_F
   return check_launch("per_token_group_quant_fp8");
 }
 
