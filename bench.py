@@ -3,22 +3,30 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (N = 1 and every N): the four Llama-3-8B-shaped block-FP8 linears -- qkv
-(6144x4096), o_proj (4096x4096), gate_up (28672x4096), down (4096x14336) -- at M = 8192
-rows. One step = per-token-group quantisation + block-FP8 GEMM for each of the four, i.e.
-one pass of the quantised-linear hot path over one batch. Inputs are seeded synthetic
-tensors (N(0,1) activations with 1% outlier channels x20, N(0, 0.02^2) weights
-block-quantised 128x128); there is no dataset. With N > 1 every rank processes its own
-batch (no data-path collective: weak scaling); the tensor-/expert-parallel variants are
-reported as extra keys.
+Headline workload (every N): the four Llama-3-70B-shaped block-FP8 linears at M = 4096 rows --
+column-parallel qkv (10240x8192) and gate_up (57344x8192), row-parallel o_proj (8192x8192) and
+down (8192x28672) -- partitioned over the N ranks as a tensor-parallel group (N = 1: un-sharded).
+One pass = per-token-group quantisation + block-FP8 GEMM for each of the four; on N > 1 the
+row-parallel layers end in the bf16 all-reduce, fused with the GEMM over NVLink peer memory.
+The total work is fixed as N grows (strong scaling). One *step* is ``inner_repeats`` passes,
+chosen so that the timed region lasts about two seconds (a sustained, power-capped number rather
+than a burst); the repeat count is printed in ``config``.
 
-`value`    TFLOP/s (2*M*N*K summed over the four GEMMs, all ranks) with inputs resident in HBM.
-`e2e`      the same metric through the public operators with HOST buffers: pinned host ->
-           device copy of the activations and device -> host copy of the outputs inside
-           the timed region, every step.
-`roofline` the GEMM kernel's achieved TFLOP/s (CUDA events around its launches in the timed
-           steps) against 2 x the measured dense bf16 rate (FP8 issues at twice the bf16 rate;
-           MEASURED_PEAKS.json holds no FP8 entry).
+Every timed item is checked first: sampled rows and columns of its output are compared with the
+CPU oracle of the un-sharded layer (relative Frobenius error <= 1e-2) and the device status word
+must be clear; an item that fails is reported as failed, not timed.
+
+`value`    TFLOP/s (2*M*N*K summed over the four GEMMs of the un-sharded layers) with inputs
+           resident in HBM; device time, max over ranks.
+`e2e`      the same metric through the public operators with HOST buffers: pinned host -> device
+           copies of the activations and device -> host copies of the outputs inside the timed
+           region, every pass.
+`roofline` the GEMM kernel's achieved TFLOP/s per GPU (CUDA events around its launches in the
+           timed steps) against an FP8 tensor peak measured in this process (torch._scaled_mm,
+           per-tensor scales, 8192^3: burst and seconds-long sustained); the fractions of
+           2 x the bf16 rates of MEASURED_PEAKS.json and of the nominal 4.5 PFLOP/s are printed too.
+`comparators` (N = 1) the same block-scaled GEMM through FlashInfer's CUTLASS sm100 kernel and
+           vLLM's CUTLASS sm100 kernel, when those libraries load.
 `cpu_baseline` the oracle's torch-native restatement of the reference path on the host cores,
            on a bounded sample (fewer rows) of the same workload.
 `--impl reference` times that CPU path alone.
@@ -27,6 +35,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -42,23 +51,31 @@ if "reference" in sys.argv and os.environ.get("OMP_NUM_THREADS") == "1":
 
 import torch  # noqa: E402
 
-M_ROWS = 8192
-GEMM_TRAFFIC_RATIO = 1.10  # measured DRAM bytes / algorithmic bytes of the GEMM kernel (ncu, see profiles/)
-LINEARS = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
-FLOPS_PER_ROW = sum(2 * n * k for _, n, k in LINEARS)
-WORKLOAD = "llama3-8b block-fp8 linears (qkv,o_proj,gate_up,down), M=8192: quant + GEMM each"
+M_ROWS = 4096
+TOL = 1e-2
+CHUNKS = 8  # every layer is defined as 8 seeded chunks along its sharded dimension, whatever N is
+# name: (N, K, how it is sharded)
+TP_LINEARS = [("qkv", 10240, 8192, "column"), ("gate_up", 57344, 8192, "column"),
+              ("o_proj", 8192, 8192, "row"), ("down", 8192, 28672, "row")]
+LLAMA8B_LINEARS = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
+FLOPS_PER_ROW = sum(2 * n * k for _, n, k, _ in TP_LINEARS)
+WORKLOAD = ("llama3-70b block-fp8 linears (qkv, gate_up column-parallel; o_proj, down row-parallel + all-reduce), "
+            "M=4096, TP = number of GPUs: quant + GEMM each")
+NVLINK_GBS = 770.0  # measured peer copy per direction per GPU on this pool (nominal 900)
+NOMINAL_FP8 = 4500.0
 
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"],
+                    bf16_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
     return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
-    """SM clock and throttle reasons sampled every ~5 ms (NVML) while a timed region runs."""
+    """SM clock, power and throttle reasons sampled every ~5 ms (NVML) while a timed region runs."""
 
     REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
@@ -104,33 +121,7 @@ class ClockSampler:
                 "power_w_max": max(self.power) if self.power else None, "source": "nvml"}
 
 
-def build_workload(device, rank: int):
-    """Seeded CPU tensors -> pinned host copies + device copies. Seeds: 2000 + index (+ rank)."""
-    from sglang_b200 import synthetic
-
-    acts_host, acts_dev, weights = {}, {}, {}
-    for i, (name, n, k) in enumerate(LINEARS):
-        x = synthetic.activation(M_ROWS, k, 2000 + 10 * i + 100 * rank).pin_memory()
-        acts_host[name] = x
-        acts_dev[name] = x.to(device, non_blocking=True)
-        weights[name] = synthetic.weight(n, k, 2001 + 10 * i, device=device)
-    torch.cuda.synchronize()
-    return acts_host, acts_dev, weights
-
-
-def run_step(S, acts, weights, gemm_events=None):
-    outs = {}
-    for name, n, k in LINEARS:
-        wq, ws = weights[name]
-        q, s = S.per_token_group_quant_fp8(acts[name], 128, column_major_scales=True)
-        if gemm_events is not None:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        outs[name] = S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)
-        if gemm_events is not None:
-            e1.record()
-            gemm_events.append((name, e0, e1))
-    return outs
+# ------------------------------------------------------------------------------ plumbing
 
 
 def dist_max(value: float, world: int, device) -> float:
@@ -147,92 +138,37 @@ def barrier(world: int):
     torch.cuda.synchronize()
 
 
-def cpu_linears(rows: int, threads: int, weights_cpu, acts_cpu):
-    """One pass of the four linears through the oracle (torch-native reference restatement)."""
-    import oracle as O
-
-    torch.set_num_threads(threads)
-    for name, n, k in LINEARS:
-        wq, ws = weights_cpu[name]
-        O.w8a8_block_fp8_linear(acts_cpu[name][:rows], wq, ws, output_dtype=torch.bfloat16)
-
-
-def cpu_inputs(rows: int):
-    """Same seeds as the GPU workload; weights quantised by the package's quantiser (bit-identical
-    to the oracle's, see tests)."""
-    from sglang_b200 import synthetic
-
-    acts, weights = {}, {}
-    for i, (name, n, k) in enumerate(LINEARS):
-        acts[name] = synthetic.activation(rows, k, 2000 + 10 * i)
-        weights[name] = synthetic.weight(n, k, 2001 + 10 * i)
-    return acts, weights
+def agree(flag: bool, world: int, device) -> bool:
+    """Rank 0's verdict, on every rank (so that all ranks take the same branch)."""
+    if world == 1:
+        return flag
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+    torch.distributed.broadcast(t, src=0)
+    return bool(t.item())
 
 
-def time_cpu_baseline(budget_s: float = 15.0):
-    """Oracle on the host cores on a bounded row sample sized to ~budget_s of CPU work."""
-    threads = os.cpu_count() or 1
-    rows = 64
-    acts, weights = cpu_inputs(4096)
-    t0 = time.perf_counter()
-    cpu_linears(rows, threads, weights, acts)
-    dt = time.perf_counter() - t0
-    # scale the sample towards the budget (the first pass doubles as warm-up)
-    rows = int(max(64, min(4096, rows * budget_s / max(dt, 1e-3) / 2)))
-    rows = rows // 32 * 32
-    t0 = time.perf_counter()
-    cpu_linears(rows, threads, weights, acts)
-    dt = time.perf_counter() - t0
-    return {"value": rows * FLOPS_PER_ROW / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": f"the four linears on the first {rows} of {M_ROWS} rows, one pass, {dt:.1f} s (torch fp32, oracle/)"}
+def device_status_clear(world: int, device) -> bool:
+    """True when no rank's device status word reports an expired wait."""
+    from sglang_b200 import _native
+
+    torch.cuda.synchronize()
+    return dist_max(float(_native.read_device_status()), world, device) == 0.0
 
 
-def run_reference(args, rank: int):
-    """The reference's CPU implementation of the path (its torch-native functions, restated in
-    oracle/ and pinned to them by the golden vectors) on all host threads."""
-    if rank != 0:
-        return
-    threads = os.cpu_count() or 1
-    acts, weights = cpu_inputs(2048)
-    # Size the step from one probe pass: about 1.5 s of host work per step (less when many steps are asked
-    # for, so that the whole run stays near two minutes), at least 64 rows. Larger samples amortise the
-    # per-call weight dequantisation the way the full 8192-row workload does.
-    cpu_linears(64, threads, weights, acts)
-    cpu_linears(256, threads, weights, acts)
-    t1 = time.perf_counter()
-    cpu_linears(256, threads, weights, acts)
-    per_256 = time.perf_counter() - t1
-    target = min(1.5, 120.0 / max(1, args.steps + args.warmup))
-    rows = int(max(64, min(2048, 256 * target / max(per_256, 1e-3)))) // 32 * 32
-    for _ in range(args.warmup):
-        cpu_linears(rows, threads, weights, acts)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_linears(rows, threads, weights, acts)
-    dt = (time.perf_counter() - t0) / args.steps
-    v = rows * FLOPS_PER_ROW / dt / 1e12
-    sample = f"each step = the four linears on {rows} of {M_ROWS} rows (torch fp32 on {threads} threads)"
-    print(json.dumps({
-        "impl": "reference", "metric": "block-FP8 GEMM TFLOPS", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 weights+activations, fp32 accumulate (emulated in fp32 on CPU)",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "rows_per_step": rows},
-        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
-
-
-NVLINK_GBS = 770.0  # measured peer copy per direction per GPU on this pool (nominal 900)
-
-
-def roofline_frac(ms: float, flops: float, hbm_bytes: float = 0.0, link_bytes: float = 0.0) -> dict:
-    """Measured time against max(flops / FP8 peak, HBM bytes / copy rate, NVLink bytes / link rate), per GPU;
-    FP8 peak = 2 x the measured sustained dense bf16 rate."""
-    peaks = load_peaks()
-    terms = {"tensor": flops / (2 * peaks["bf16_sustained"] * 1e12), "hbm": hbm_bytes / (peaks["hbm_gbs"] * 1e9),
-             "nvlink": link_bytes / (NVLINK_GBS * 1e9)}
-    bound = max(terms, key=terms.get)
-    return {"roofline_frac": terms[bound] / (ms * 1e-3), "roofline_bound": bound}
+def timed(fn, n: int, world: int, device, warm: int = 2) -> float:
+    """Device milliseconds per call of ``fn``, max over ranks. The ranks meet at a barrier first: the
+    peer-memory handshakes inside ``fn`` wait two seconds at most for a rank that is still busy."""
+    barrier(world)
+    for _ in range(warm):
+        fn()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    barrier(world)
+    return dist_max(e0.elapsed_time(e1) / n, world, device)
 
 
 def graph_time_us(fns, rounds: int = 5) -> float:
@@ -258,6 +194,416 @@ def graph_time_us(fns, rounds: int = 5) -> float:
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) * 1e3 / len(fns))
     return sorted(times)[len(times) // 2]
+
+
+def roofline_frac(ms: float, flops: float, hbm_bytes: float = 0.0, link_bytes: float = 0.0, fp8_peak=None) -> dict:
+    """Measured time against max(flops / FP8 peak, HBM bytes / copy rate, NVLink bytes / link rate), per GPU."""
+    peaks = load_peaks()
+    fp8 = fp8_peak or 2 * peaks["bf16_sustained"]
+    terms = {"tensor": flops / (fp8 * 1e12), "hbm": hbm_bytes / (peaks["hbm_gbs"] * 1e9),
+             "nvlink": link_bytes / (NVLINK_GBS * 1e9)}
+    bound = max(terms, key=terms.get)
+    return {"roofline_frac": terms[bound] / (ms * 1e-3), "roofline_bound": bound}
+
+
+# ------------------------------------------------------------------- measured FP8 tensor peak
+
+
+def measure_fp8_peak(device, local_rank: int, sustain_s: float = 2.0) -> dict:
+    """Dense FP8 rate of the library GEMM on this GPU: torch._scaled_mm (cuBLASLt), E4M3 x E4M3 -> bf16,
+    per-tensor scales, 8192^3. ``burst`` = best of 10 single launches, ``sustained`` = a back-to-back loop of
+    at least ``sustain_s`` seconds, each with the SM clock sampled while it ran."""
+    try:
+        n = 8192
+        g = torch.Generator(device=device).manual_seed(11)
+        a = torch.randn(n, n, device=device, generator=g).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device, generator=g).to(torch.float8_e4m3fn).t()  # column-major operand
+        one = torch.ones((), device=device)
+
+        def mm():
+            return torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+        for _ in range(3):
+            mm()
+        torch.cuda.synchronize()
+        flops = 2.0 * n * n * n
+        best = float("inf")
+        with ClockSampler(local_rank) as c_burst:
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                mm()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+        per = max(best, 0.05)
+        loops = int(sustain_s * 1e3 / per) + 1
+        with ClockSampler(local_rank) as c_sus:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(loops):
+                mm()
+            e1.record()
+            torch.cuda.synchronize()
+        sus_ms = e0.elapsed_time(e1)
+        return {"burst_tflops": flops / best / 1e9, "sustained_tflops": flops * loops / sus_ms / 1e9,
+                "sustained_seconds": sus_ms / 1e3, "burst_clocks": c_burst.summary(), "sustained_clocks": c_sus.summary(),
+                "how": "torch._scaled_mm e4m3 x e4m3 -> bf16, per-tensor scales, 8192^3, CUDA events"}
+    except Exception as e:
+        return {"unavailable": repr(e)}
+
+
+# --------------------------------------------------------------------- the tensor-parallel layers
+
+
+def tp_chunk(i: int, n: int, k: int, kind: str, c: int, device):
+    """Chunk ``c`` of layer ``i``, drawn on the device from its own seed and block-quantised: rows
+    ``[c*n/8, ..)`` of a column-parallel weight, K columns ``[c*k/8, ..)`` of a row-parallel one. Chunk edges are
+    multiples of 128, so quantising chunk by chunk equals quantising the whole weight."""
+    from sglang_b200.weight_quant import block_quant_weight_fp8
+
+    g = torch.Generator(device=device).manual_seed(3000 + 100 * i + c)
+    shape = (n // CHUNKS, k) if kind == "column" else (n, k // CHUNKS)
+    w = (torch.randn(shape, generator=g, device=device) * 0.02).bfloat16()
+    return block_quant_weight_fp8(w)
+
+
+def tp_shard(i: int, n: int, k: int, kind: str, rank: int, world: int, device):
+    per = CHUNKS // world
+    parts = [tp_chunk(i, n, k, kind, c, device) for c in range(rank * per, (rank + 1) * per)]
+    dim = 0 if kind == "column" else 1
+    return (torch.cat([p[0] for p in parts], dim).contiguous(), torch.cat([p[1] for p in parts], dim).contiguous())
+
+
+def tp_activation(i: int, k: int, device, rows: int = M_ROWS):
+    """N(0,1) with 1 % of the channels scaled x20, drawn on the device (identical on every rank)."""
+    g = torch.Generator(device=device).manual_seed(3500 + i)
+    x = torch.randn(rows, k, generator=g, device=device)
+    idx = torch.randperm(k, generator=g, device=device)[: math.ceil(0.01 * k)]
+    x[:, idx] *= 20
+    return x.bfloat16()
+
+
+def sample_rows(m: int, count: int = 32):
+    count = min(count, m)
+    step = m // count
+    return [r * step + (7 * r) % step for r in range(count)]
+
+
+def oracle_weight_sample(i: int, n: int, k: int, kind: str, device):
+    """A few 128-row blocks of the un-sharded weight of layer ``i`` for the CPU oracle: one block out of every
+    chunk for a column-parallel layer (so that every rank's shard is covered), four blocks for a row-parallel
+    one. Returns (FP8 rows [B*128, K], scales [B, K/128], the output columns they produce), on the CPU."""
+    if kind == "column":
+        per = n // CHUNKS // 128
+        wq, ws, cols = [], [], []
+        for c in range(CHUNKS):
+            q, s = tp_chunk(i, n, k, kind, c, device)
+            b = (3 * c + 1) % per
+            wq.append(q[b * 128:(b + 1) * 128].cpu())
+            ws.append(s[b:b + 1].cpu())
+            first = (c * per + b) * 128
+            cols.extend(range(first, first + 128))
+            del q, s
+        return torch.cat(wq, 0), torch.cat(ws, 0), torch.tensor(cols)
+    nb = n // 128
+    blocks = sorted({0, nb // 3, (2 * nb) // 3, nb - 1})
+    wq, ws = [], []
+    for c in range(CHUNKS):
+        q, s = tp_chunk(i, n, k, kind, c, device)
+        wq.append(torch.cat([q[b * 128:(b + 1) * 128] for b in blocks], 0).cpu())
+        ws.append(torch.cat([s[b:b + 1] for b in blocks], 0).cpu())
+        del q, s
+    cols = [b * 128 + j for b in blocks for j in range(128)]
+    return torch.cat(wq, 1), torch.cat(ws, 1), torch.tensor(cols)
+
+
+class TPLayers:
+    """This rank's shard of the four layers, their inputs, the peer-memory all-reduce objects, and (rank 0) the
+    oracle's answers on sampled rows and columns of the un-sharded layers."""
+
+    def __init__(self, S, device, rank: int, world: int, row_counts=(M_ROWS,)):
+        import oracle as O  # the checker of the sampled outputs; never on the timed path
+        from sglang_b200 import parallel as P
+
+        assert CHUNKS % world == 0, "the layers are defined as 8 chunks: run with 1, 2, 4 or 8 GPUs"
+        self.S, self.P, self.O = S, P, O
+        self.device, self.rank, self.world = device, rank, world
+        self.layers, self.ref, self.peer = [], {}, {}
+        for i, (name, n, k, kind) in enumerate(TP_LINEARS):
+            x_full = tp_activation(i, k, device)
+            wq, ws = tp_shard(i, n, k, kind, rank, world, device)
+            if kind == "row":
+                ks = k // world
+                x = x_full[:, rank * ks:(rank + 1) * ks].contiguous()
+            else:
+                x = x_full
+            self.layers.append((name, n, k, kind, x, wq, ws))
+            if rank == 0:
+                wq_s, ws_s, cols = oracle_weight_sample(i, n, k, kind, device)
+                for m in row_counts:
+                    rows = sample_rows(m)
+                    want = O.w8a8_block_fp8_linear(x_full[rows].cpu(), wq_s, ws_s, output_dtype=torch.float32)
+                    self.ref[(name, m)] = (rows, cols, want)
+            del x_full
+        torch.cuda.empty_cache()
+        barrier(world)
+
+    def peer_for(self, name: str, n: int, graph_safe: bool = False, max_tokens: int = M_ROWS):
+        from sglang_b200.peer_allreduce import PeerAllReduce
+
+        key = (name, graph_safe)
+        if key not in self.peer:
+            self.peer[key] = PeerAllReduce(max_tokens, n, torch.bfloat16, graph_safe=graph_safe)
+        return self.peer[key]
+
+    def forward(self, rows: int, mode: str, events=None, graph_safe: bool = False, inputs=None):
+        """One pass over the four layers on the first ``rows`` rows. ``mode``: "peer" (all-reduce fused with the
+        GEMM over peer memory) or "nccl". Returns the outputs (row-parallel outputs of "peer" are views of the
+        symmetric buffers: valid until the layer's next call)."""
+        S, outs = self.S, {}
+        for name, n, k, kind, x, wq, ws in self.layers:
+            xin = (inputs[name] if inputs is not None else x)[:rows]
+            q, s = S.per_token_group_quant_fp8(xin, 128, column_major_scales=True)
+            if events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            if kind == "row" and self.world > 1 and mode == "peer":
+                out, _ = self.peer_for(name, n, graph_safe, M_ROWS if not graph_safe else 16).linear(q, s, wq, ws)
+            else:
+                out = S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)
+                if kind == "row" and self.world > 1:
+                    self.P.tensor_model_parallel_all_reduce(out)
+            if events is not None:
+                e1.record()
+                events.append((name, e0, e1))
+            outs[name] = out
+        return outs
+
+    def check(self, rows: int, mode: str) -> dict:
+        """Run one pass and compare sampled rows x columns of every layer's output, as held by every rank, with
+        the oracle of the un-sharded layer. Returns {"rel_frob": worst, "checked_rows", "checked_cols", "ok"}."""
+        world, dev = self.world, self.device
+        barrier(world)
+        outs = self.forward(rows, mode)
+        torch.cuda.synchronize()
+        worst, n_rows, n_cols = 0.0, 0, 0
+        for name, n, k, kind, *_ in self.layers:
+            ridx = torch.tensor(sample_rows(rows), device=dev)
+            mine = outs[name][ridx].float()
+            if world > 1:
+                parts = [torch.empty_like(mine) for _ in range(world)]
+                torch.distributed.all_gather(parts, mine.contiguous())
+            else:
+                parts = [mine]
+            if self.rank == 0:
+                _, cols, want = self.ref[(name, rows)]
+                n_rows, n_cols = want.shape[0], n_cols + want.shape[1]
+                if kind == "column":
+                    got = [torch.cat(parts, 1).cpu()[:, cols]]
+                else:  # replicated result: every rank's copy is checked
+                    got = [p.cpu()[:, cols] for p in parts]
+                for g_ in got:
+                    err = self.O.rel_frobenius(g_, want)
+                    worst = max(worst, err if err == err else float("inf"))
+        status_ok = device_status_clear(world, dev)
+        ok = agree(worst < TOL and status_ok, world, dev)
+        return {"rel_frob": worst, "checked_rows": n_rows, "checked_cols": n_cols, "device_status_clear": status_ok,
+                "ok": ok, "against": "CPU oracle of the un-sharded layers on sampled rows x columns"}
+
+
+# --------------------------------------------------------------------------- CPU baseline legs
+
+
+def cpu_inputs(rows: int):
+    """The un-sharded layers for the host arm: same shapes and distributions, drawn and quantised on the CPU."""
+    from sglang_b200 import synthetic
+
+    acts, weights = {}, {}
+    for i, (name, n, k, _) in enumerate(TP_LINEARS):
+        acts[name] = synthetic.activation(rows, k, 2000 + 10 * i)
+        weights[name] = synthetic.weight(n, k, 2001 + 10 * i)
+    return acts, weights
+
+
+def cpu_linears(rows: int, threads: int, weights_cpu, acts_cpu):
+    """One pass of the four linears through the oracle (torch-native reference restatement)."""
+    import oracle as O
+
+    torch.set_num_threads(threads)
+    for name, n, k, _ in TP_LINEARS:
+        wq, ws = weights_cpu[name]
+        O.w8a8_block_fp8_linear(acts_cpu[name][:rows], wq, ws, output_dtype=torch.bfloat16)
+
+
+def time_cpu_baseline(budget_s: float = 15.0):
+    """Oracle on the host cores on a bounded row sample sized to ~budget_s of CPU work."""
+    threads = os.cpu_count() or 1
+    rows = 32
+    acts, weights = cpu_inputs(1024)
+    t0 = time.perf_counter()
+    cpu_linears(rows, threads, weights, acts)
+    dt = time.perf_counter() - t0
+    # scale the sample towards the budget (the first pass doubles as warm-up)
+    rows = int(max(32, min(1024, rows * budget_s / max(dt, 1e-3) / 2)))
+    rows = rows // 32 * 32
+    t0 = time.perf_counter()
+    cpu_linears(rows, threads, weights, acts)
+    dt = time.perf_counter() - t0
+    return {"value": rows * FLOPS_PER_ROW / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"the four un-sharded linears on the first {rows} of {M_ROWS} rows, one pass, {dt:.1f} s (torch fp32, oracle/)"}
+
+
+def run_reference(args, rank: int):
+    """The reference's CPU implementation of the path (its torch-native functions, restated in
+    oracle/ and pinned to them by the golden vectors) on all host threads."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    acts, weights = cpu_inputs(1024)
+    # Size the step from one probe pass: about 3 s of host work per step (less when many steps are asked for, so
+    # that the whole run stays near two minutes), at least 32 rows. Every pass dequantises the weights, as the
+    # reference's native path does per call; larger samples amortise that the way the full 4096 rows would.
+    cpu_linears(32, threads, weights, acts)
+    t1 = time.perf_counter()
+    cpu_linears(128, threads, weights, acts)
+    per_128 = time.perf_counter() - t1
+    target = min(3.0, 120.0 / max(1, args.steps + args.warmup))
+    rows = int(max(32, min(1024, 128 * target / max(per_128, 1e-3)))) // 32 * 32
+    for _ in range(args.warmup):
+        cpu_linears(rows, threads, weights, acts)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_linears(rows, threads, weights, acts)
+    dt = (time.perf_counter() - t0) / args.steps
+    v = rows * FLOPS_PER_ROW / dt / 1e12
+    sample = f"each step = the four un-sharded linears on {rows} of {M_ROWS} rows (torch fp32 on {threads} threads)"
+    print(json.dumps({
+        "impl": "reference", "metric": "block-FP8 GEMM TFLOPS", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 weights+activations, fp32 accumulate (emulated in fp32 on CPU)",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "rows_per_step": rows},
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------- 1-GPU line items
+
+
+def bench_llama8b(S, device, fp8_peak: float):
+    """BASELINE config 2: the four Llama-3-8B-shaped linears on one GPU at M = 1 ... 8192 (quant + GEMM; the
+    decode sizes appear under ``kernels`` with rotated weights). Device time from CUDA-graph replays."""
+    from sglang_b200 import synthetic
+
+    out = {}
+    for i, (name, n, k) in enumerate(LLAMA8B_LINEARS):
+        wq, ws = synthetic.weight(n, k, 2001 + 10 * i, device=device)
+        for m in (128, 1024, 8192):
+            x = synthetic.activation(m, k, 2000 + 10 * i).to(device)
+            q, s = S.per_token_group_quant_fp8(x, 128, column_major_scales=True)
+            us_lin = graph_time_us([lambda: S.w8a8_block_fp8_linear(x, wq, [128, 128], ws)] * 4)
+            us_mm = graph_time_us([lambda: S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)] * 4)
+            fl = 2.0 * m * n * k
+            nbytes = m * k + n * k + 2 * m * n + 4 * (m * k // 128 + n * k // 16384)
+            out[f"{name}_M{m}"] = {"N": n, "K": k, "linear_us": us_lin, "gemm_us": us_mm,
+                                   "gemm_tflops": fl / us_mm / 1e6, "linear_tflops": fl / us_lin / 1e6,
+                                   **roofline_frac(us_mm * 1e-3, fl, nbytes, fp8_peak=fp8_peak)}
+        del wq, ws
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_comparators(S, device):
+    """The block-scaled FP8 GEMM of the libraries the reference calls on this GPU, on the same operands as ours:
+    FlashInfer ``gemm_fp8_nt_groupwise`` (CUTLASS sm100 blockwise kernel, 1-SM and 2-SM MMA) and vLLM's
+    ``cutlass_scaled_mm`` (CUTLASS sm100 blockwise kernel). Bench-only: the package never imports them. An entry
+    says ``unavailable`` with the reason when a library or its compiled module is missing."""
+    from sglang_b200 import synthetic
+
+    shapes = [("llama8b_" + n_, 8192, n, k) for n_, n, k in LLAMA8B_LINEARS]
+    shapes += [("llama70b_" + n_, M_ROWS, n, k) for n_, n, k, _ in TP_LINEARS]
+
+    def rel(a, b):
+        a, b = a.float(), b.float()
+        return float((a - b).norm() / b.norm())
+
+    fi_mod, fi_err = None, None
+    try:
+        os.environ.setdefault("FLASHINFER_WORKSPACE_BASE", os.path.join(ROOT, "baseline", "_ref", "fi"))
+        os.environ.setdefault("FLASHINFER_CUDA_ARCH_LIST", "10.0a")
+        from flashinfer.gemm.gemm_base import gen_gemm_sm100_module
+
+        spec = gen_gemm_sm100_module()
+        so = str(spec.jit_library_path)
+        if not os.path.exists(so):
+            raise RuntimeError("the sm100 GEMM module of flashinfer is not prebuilt (it is JIT-compiled; no build "
+                               "is attempted inside the benchmark)")
+        fi_mod = spec.load(so)
+        fi_ws = torch.empty(32 * 1024 * 1024, dtype=torch.uint8, device=device)
+    except Exception as e:
+        fi_err = repr(e)[:300]
+    vllm_err = None
+    try:
+        import vllm._C  # noqa: F401
+        vllm_mm = torch.ops._C.cutlass_scaled_mm
+    except Exception as e:
+        vllm_err = repr(e)[:300]
+
+    out = {}
+    for i, (label, m, n, k) in enumerate(shapes):
+        g = torch.Generator(device=device).manual_seed(8100 + i)
+        x = torch.randn(m, k, device=device, generator=g).bfloat16()
+        wq, ws = synthetic.block_quant_weight_fp8((torch.randn(n, k, device=device, generator=g) * 0.02).bfloat16())
+        q, s = S.per_token_group_quant_fp8(x, 128, column_major_scales=True)  # s: [m, k/128], stride (1, m)
+        ours = S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)
+        fl = 2.0 * m * n * k
+        item = {"M": m, "N": n, "K": k}
+        us = graph_time_us([lambda: S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)] * 4)
+        item["ours"] = {"us": us, "tflops": fl / us / 1e6}
+        for mma_sm in (1, 2):
+            key = f"flashinfer_cutlass_sm100_{mma_sm}sm"
+            if fi_mod is None:
+                item[key] = {"unavailable": fi_err}
+                continue
+            try:
+                a_sc = s.t().contiguous() if not s.t().is_contiguous() else s.t()  # [k/128, m]
+                b_sc = ws.t().contiguous()                                            # [k/128, n/128]
+                o = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+
+                def call():
+                    fi_mod.gemm_fp8_nt_groupwise(fi_ws, q, wq, a_sc, b_sc, o, 1, 128, 128, "MN", mma_sm)
+
+                call()
+                torch.cuda.synchronize()
+                us = graph_time_us([call] * 4)
+                item[key] = {"us": us, "tflops": fl / us / 1e6, "rel_frob_vs_ours": rel(o, ours)}
+            except Exception as e:
+                item[key] = {"unavailable": repr(e)[:300]}
+                torch.cuda.synchronize()
+        key = "vllm_cutlass_sm100"
+        if vllm_err is not None:
+            item[key] = {"unavailable": vllm_err}
+        else:
+            try:
+                o = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+                b_t, sb_t = wq.t(), ws.t()
+
+                def call():
+                    vllm_mm(o, q, b_t, s, sb_t, None)
+
+                call()
+                torch.cuda.synchronize()
+                us = graph_time_us([call] * 4)
+                item[key] = {"us": us, "tflops": fl / us / 1e6, "rel_frob_vs_ours": rel(o, ours)}
+            except Exception as e:
+                item[key] = {"unavailable": repr(e)[:300]}
+                torch.cuda.synchronize()
+        out[label] = item
+        del x, wq, ws, q, s, ours
+    torch.cuda.empty_cache()
+    return out
 
 
 def bench_kernels(S, device):
@@ -289,7 +635,7 @@ def bench_kernels(S, device):
     us = graph_time_us([lambda: S.moe_align_block_size(ids, 128, E)] * 4)
     max_pad = T * topk + (E + 1) * 127
     out["moe_align_block_size_16384x8_E256"] = item(us, T * topk * 4 + 4 * (max_pad + max_pad // 128 + E + 3))
-    for name, n, k in LINEARS:
+    for name, n, k in LLAMA8B_LINEARS:
         copies = max(3, -(-400_000_000 // (n * k)))
         ws = [torch.randn(n, k, device=device, generator=g).to(fp8) for _ in range(copies)]
         wscale = torch.rand(n // 128, k // 128, device=device, generator=g)
@@ -304,172 +650,273 @@ def bench_kernels(S, device):
     return out
 
 
-def bench_moe(S, device, steps: int):
-    """Extra line items: fused-MoE tokens/s for the DeepSeek-V3 and Mixtral shaped layers (1 GPU)."""
+def moe_reference_rows(O, cfg, x, tw, ti, rows, seed: int, device):
+    """Oracle output of the MoE layer for the tokens ``rows`` (a token's result does not depend on the other
+    tokens). The experts those tokens use are drawn again from their per-expert seeds and taken to the CPU."""
+    from sglang_b200 import synthetic
+
+    ridx = torch.tensor(rows, device=ti.device)
+    used = torch.unique(ti[ridx].flatten()).long()
+    local = torch.searchsorted(used, ti[ridx].long()).to(torch.int32)
+    parts = [synthetic.expert_weights(1, cfg["I"], cfg["H"], seed, device=device, first_expert=int(e)) for e in used.tolist()]
+    w1, w2, w1_s, w2_s = (torch.cat([p[j] for p in parts], 0).cpu() for j in range(4))
+    del parts
+    return O.fused_experts_fp8(x[ridx].cpu(), w1, w2, w1_s, w2_s, tw[ridx].cpu().float(), local.cpu(), [128, 128])
+
+
+def moe_inputs(cfg, T: int, device, seed: int = 5000):
+    """Tokens and routing of one MoE line item (identical on every rank): N(0,1) tokens; DeepSeek-V3: N(0,1)
+    logits through the biased grouped top-k; Mixtral: N(0,1) logits plus a Zipf(1.2) per-expert bias, softmax top-2."""
     from sglang_b200 import synthetic
     from sglang_b200.topk import biased_grouped_topk, fused_topk
 
+    E, topk, H = cfg["E"], cfg["topk"], cfg["H"]
+    g = torch.Generator().manual_seed(seed + T)
+    x = torch.randn(T, H, generator=g).bfloat16().to(device)
+    if "n_group" in cfg:
+        logits = torch.randn(T, E, generator=g).to(device)
+        tw, ti = biased_grouped_topk(x, logits, torch.zeros(E, device=device), topk, True, cfg["n_group"], cfg["topk_group"])
+    else:
+        logits = synthetic.zipf_router_logits(T, E, seed + 1).to(device)
+        tw, ti = fused_topk(x, logits, topk, True)
+    return x, tw, ti
+
+
+def bench_moe(S, device, steps: int, fp8_peak: float):
+    """Extra line items: fused-MoE tokens/s for the DeepSeek-V3 and Mixtral shaped layers on one GPU at every
+    token count of BASELINE configs 4 and 5; each checked on sampled tokens against the oracle first."""
+    import oracle as O
+    from sglang_b200 import synthetic
+
     out = {}
-    for label, cfg, T in (("deepseek_v3_T16384", synthetic.DEEPSEEK_V3, 16384), ("mixtral_8x7b_T8192", synthetic.MIXTRAL, 8192)):
+    for label, cfg, Ts in (("deepseek_v3", synthetic.DEEPSEEK_V3, (16384, 2048, 128, 1)),
+                           ("mixtral_8x7b", synthetic.MIXTRAL, (8192, 1024, 64, 1))):
         E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
-        w1, w2, w1_s, w2_s = synthetic.expert_weights(E, I, H, 4000 + E, device=device)
-        g = torch.Generator().manual_seed(5000 + T)
-        x = torch.randn(T, H, generator=g).bfloat16().to(device)
-        if E == 256:
-            logits = torch.randn(T, E, generator=g).to(device)
-            tw, ti = biased_grouped_topk(x, logits, torch.zeros(E, device=device), topk, True, cfg["n_group"], cfg["topk_group"])
-        else:
-            logits = synthetic.zipf_router_logits(T, E, 5001).to(device)
-            tw, ti = fused_topk(x, logits, topk, True)
+        seed = 4000 + E
+        w1, w2, w1_s, w2_s = synthetic.expert_weights(E, I, H, seed, device=device)
         conf = S.MoeRunnerConfig(inplace=False)
-        topk_out = S.StandardTopKOutput(tw, ti, None)
+        for T in Ts:
+            x, tw, ti = moe_inputs(cfg, T, device)
+            topk_out = S.StandardTopKOutput(tw, ti, None)
 
-        def call():
-            return S.fused_experts(x, w1, w2, topk_out, conf, use_fp8_w8a8=True, w1_scale=w1_s, w2_scale=w2_s, block_shape=[128, 128])
+            def call():
+                return S.fused_experts(x, w1, w2, topk_out, conf, use_fp8_w8a8=True, w1_scale=w1_s, w2_scale=w2_s,
+                                       block_shape=[128, 128])
 
-        for _ in range(3):
-            call()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            call()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        active = int(torch.unique(ti).numel())
-        moe_bytes = 4 * T * H + 3 * H * I * active * (1 + 4 / 16384) + 8 * T * topk
-        out[label] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "tflops": 6 * T * topk * H * I / ms / 1e9,
-                      **roofline_frac(ms, 6 * T * topk * H * I, moe_bytes),
-                      "config": {"E": E, "topk": topk, "H": H, "I": I, "T": T, "weights_mb": (w1.numel() + w2.numel()) / 1e6}}
+            got = call()
+            rows = sample_rows(T, 4 if T == Ts[0] else 2)
+            want = moe_reference_rows(O, cfg, x, tw, ti, rows, seed, device)
+            err = O.rel_frobenius(got[rows].float().cpu(), want)
+            parity = {"rel_frob": err, "checked_rows": len(rows), "device_status_clear": device_status_clear(1, device),
+                      "ok": bool(err < TOL)}
+            key = f"{label}_T{T}"
+            if not (parity["ok"] and parity["device_status_clear"]):
+                out[key] = {"error": "parity check failed; not timed", "parity": parity}
+                continue
+            if T >= 1024:
+                for _ in range(3):
+                    call()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(steps):
+                    call()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / steps
+            else:
+                ms = graph_time_us([call] * 4) * 1e-3  # a server replays decode steps from a graph
+            active = int(torch.unique(ti).numel())
+            moe_bytes = 4 * T * H + 3 * H * I * active * (1 + 4 / 16384) + 8 * T * topk
+            out[key] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "tflops": 6 * T * topk * H * I / ms / 1e9,
+                        "hbm_gbs_on_algorithmic_bytes": moe_bytes / ms / 1e6,
+                        **roofline_frac(ms, 6 * T * topk * H * I, moe_bytes, fp8_peak=fp8_peak), "parity": parity,
+                        "config": {"E": E, "topk": topk, "H": H, "I": I, "T": T, "experts_touched": active}}
         del w1, w2, w1_s, w2_s
         torch.cuda.empty_cache()
     return out
 
 
-def bench_parallel(S, device, rank: int, world: int, steps: int):
-    """Extra line items at N > 1: Llama-3-70B-shaped tensor-parallel linears (M = 4096; column-parallel
-    qkv + gate_up, row-parallel o_proj + down with the bf16 all-reduce) and the DeepSeek-V3-shaped MoE
-    layer expert-parallel over the N ranks (T = 16384 tokens in total; "standard" = replicated tokens +
-    all-reduce, "a2a" = tokens partitioned + all-to-all dispatch / combine). Device time, max over ranks."""
-    from sglang_b200 import parallel as P
-    from sglang_b200 import synthetic
-    from sglang_b200.topk import biased_grouped_topk
+# ---------------------------------------------------------------------- N > 1 line items
 
-    def timed(fn, n):
-        for _ in range(2):
-            fn()
-        barrier(world)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        barrier(world)
-        return dist_max(e0.elapsed_time(e1) / n, world, device)
 
+def bench_tp_items(tp: TPLayers, world: int, device, steps: int, fp8_peak: float):
+    """BASELINE config 3 at M = 32 / 512 / 4096 with the all-reduce by NCCL or fused with the GEMM over peer
+    memory, plus the decode-sized step replayed from a CUDA graph. Every item is checked against the oracle of
+    the un-sharded layers before it is timed."""
     out = {}
-    M = 4096
-    layers, flops = [], 0
-    for i, (name, (n, k, kind)) in enumerate(synthetic.LLAMA3_70B_TP_LINEARS.items()):
-        g = torch.Generator(device=device).manual_seed(3000 + i)
-        # each rank draws only its own shard (same values as slicing a full tensor would need 0.5 GB per layer on every rank)
-        if kind == "column":
-            w = (torch.randn(n // world, k, generator=g, device=device) * 0.02).bfloat16()
-            x = torch.randn(M, k, generator=g, device=device).bfloat16()
-        else:
-            w = (torch.randn(n, k // world, generator=g, device=device) * 0.02).bfloat16()
-            x = torch.randn(M, k // world, generator=g, device=device).bfloat16()
-        wq, ws = synthetic.block_quant_weight_fp8(w)
-        layers.append((kind, x, wq, ws))
-        flops += 2 * M * n * k
-    del w
-
-    from sglang_b200.peer_allreduce import PeerAllReduce
-
-    # row-parallel layers share one set of peer buffers per output width (N = 8192 for both)
-    peer = {}
-    for kind, x, wq, ws in layers:
-        if kind == "row" and wq.shape[0] not in peer:
-            peer[wq.shape[0]] = PeerAllReduce(M, wq.shape[0], torch.bfloat16)
-
-    def tp_step(rows: int, fused: bool):
-        for kind, x, wq, ws in layers:
-            if kind == "row" and fused:
-                peer[wq.shape[0]].linear_bf16_input(x[:rows], wq, ws)
+    w_bytes = sum(wq.numel() for *_, wq, _ in tp.layers)
+    for rows in (M_ROWS, 512, 32):
+        for mode in ("nccl", "peer"):
+            key = f"tp_llama70b_M{rows}" + ("_peer_fused" if mode == "peer" else "_nccl")
+            parity = tp.check(rows, mode)
+            if not parity["ok"]:
+                out[key] = {"error": "parity check failed; not timed", "parity": parity, "tp": world}
                 continue
-            y = S.w8a8_block_fp8_linear(x[:rows], wq, [128, 128], ws)
-            if kind == "row":
-                P.tensor_model_parallel_all_reduce(y)
-
-    # prefill-sized (M = 4096) and decode-sized (M = 16) steps, all-reduce by NCCL or fused with the
-    # GEMM over peer memory (fan-out epilogue + finishing kernel)
-    for rows in (M, 16):
-        for fused in (False, True):
-            ms = timed(lambda: tp_step(rows, fused), steps)
-            key = f"tp_llama70b_M{rows}" + ("_peer_fused" if fused else "")
-            # per GPU: 1/world of the flops, its weight shard streamed once, 2 all-reduces of [rows, 8192] bf16
-            w_bytes = sum(wq.numel() for _, _, wq, _ in layers)
-            out[key] = {"tflops": flops * rows / M / ms / 1e9, "ms": ms, "tp": world,
-                        "allreduce": "peer memory, fused with the GEMM" if fused else "nccl",
+            ms = timed(lambda: tp.forward(rows, mode), steps, world, device)
+            fl = FLOPS_PER_ROW * rows
+            out[key] = {"tflops": fl / ms / 1e9, "ms": ms, "tp": world, "parity": parity,
+                        "allreduce": "peer memory, fused with the GEMM" if mode == "peer" else "nccl",
                         "allreduce_bytes_per_step": 2 * rows * 8192 * 2,
-                        **roofline_frac(ms, flops * rows / M / world, w_bytes,
-                                        2 * (world - 1) / world * 2 * rows * 8192 * 2)}
-    del peer
-    # the decode-sized step again, replayed from a CUDA graph (how a server runs decode): the peer
-    # path uses device-side epochs and a single slot buffer so that the capture can be replayed
-    peer = {n_: PeerAllReduce(16, n_, torch.bfloat16, graph_safe=True)
-            for n_ in {wq.shape[0] for kind, _, wq, _ in layers if kind == "row"}}
-    for fused in (False, True):
-        key = "tp_llama70b_M16_graph" + ("_peer_fused" if fused else "")
+                        **roofline_frac(ms, fl / world, w_bytes, 2 * (world - 1) / world * 2 * rows * 8192 * 2,
+                                        fp8_peak=fp8_peak)}
+    # the decode-sized step (M = 16) replayed from a CUDA graph (how a server runs decode): the peer path then
+    # keeps its epochs on the device and uses a single slot buffer so that the capture can be replayed
+    for mode in ("nccl", "peer"):
+        key = "tp_llama70b_M16_graph" + ("_peer_fused" if mode == "peer" else "_nccl")
         try:
             stream = torch.cuda.Stream()
             graph = torch.cuda.CUDAGraph()
+            barrier(world)
             with torch.cuda.stream(stream):
-                tp_step(16, fused)
+                tp.forward(16, mode, graph_safe=True)
                 torch.cuda.synchronize()
                 barrier(world)
                 with torch.cuda.graph(graph, stream=stream):
-                    tp_step(16, fused)
-            ms = timed(graph.replay, steps)
-            out[key] = {"ms": ms, "tp": world, "allreduce": "peer memory, fused with the GEMM" if fused else "nccl"}
+                    tp.forward(16, mode, graph_safe=True)
+            ms = timed(graph.replay, steps, world, device)
+            out[key] = {"ms": ms, "tp": world, "device_status_clear": device_status_clear(world, device)}
         except Exception as e:  # a capture that fails must not take the other line items with it
-            out[key] = {"error": repr(e)}
+            out[key] = {"error": repr(e)[:300]}
             torch.cuda.synchronize()
             barrier(world)
-    del peer
-    del layers
+    return out
+
+
+def bench_moe_parallel(S, device, rank: int, world: int, steps: int, fp8_peak: float):
+    """BASELINE config 5 (DeepSeek-V3 layer, experts partitioned over the ranks, T = 16384 / 2048 / 128 / 1 tokens
+    in total) in three forms -- "standard" (tokens replicated, all-reduce), all-to-all through NCCL, all-to-all
+    through this package's peer-memory kernels -- and config 4 (Mixtral layer, intermediate dimension split over
+    the ranks, all-reduce). Before an item is timed its output is compared with the oracle on sampled tokens (and
+    the all-to-all forms with the standard form on every token)."""
+    import oracle as O
+    from sglang_b200 import parallel as P
+    from sglang_b200 import synthetic
+
+    out = {}
+
+    def sampled(result_rows, tokens, offset, count):
+        """Rows of ``tokens`` from a result that holds tokens [offset, offset + count): summed over ranks so that
+        every rank (and the checker on rank 0) sees all of them."""
+        buf = torch.zeros(len(tokens), result_rows.shape[1], dtype=torch.float32, device=device)
+        for j, t in enumerate(tokens):
+            if offset <= t < offset + count:
+                buf[j] = result_rows[t - offset].float()
+        if world > 1:
+            torch.distributed.all_reduce(buf)
+        return buf
+
+    # ---- expert parallel, DeepSeek-V3
+    cfg = synthetic.DEEPSEEK_V3
+    E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
+    el, seed = E // world, 4000 + E
+    w1, w2, w1_s, w2_s = synthetic.expert_weights(el, I, H, seed, device=device, first_expert=rank * el)
+    for T in (16384, 2048, 128, 1):
+        x, tw, ti = moe_inputs(cfg, T, device)
+        tokens = sample_rows(T, 4 if T == 16384 else 2)
+        want = moe_reference_rows(O, cfg, x, tw, ti, tokens, seed, device) if rank == 0 else None
+        per = -(-T // world)
+        lo, hi = min(T, rank * per), min(T, (rank + 1) * per)
+        full_std = None
+        modes = (("ep", "standard"), ("ep_a2a", "a2a_nccl"), ("ep_peer", "a2a_peer_memory"))
+        if T < world:  # fewer tokens than ranks: nothing to partition, only the replicated form applies
+            modes = modes[:1]
+        for mode, label in modes:
+            key = f"ep_deepseek_v3_T{T}_{label}"
+            try:
+                layer = P.FusedMoE(w1, w2, w1_s, w2_s, rank, world, mode=mode, presharded=True, num_experts=E,
+                                   max_tokens=max(per, 1))
+                if mode == "ep":
+                    xs, ws_, is_ = x, tw, ti
+                    off, cnt = 0, T
+                else:
+                    xs, ws_, is_ = x[lo:hi].contiguous(), tw[lo:hi].contiguous(), ti[lo:hi].contiguous()
+                    off, cnt = lo, hi - lo
+                barrier(world)
+                got = layer(xs, ws_, is_)
+                torch.cuda.synchronize()
+                rows_got = sampled(got, tokens, off, cnt if mode != "ep" else T)
+                if mode == "ep" and world > 1:
+                    rows_got /= world  # every rank contributed the same replicated rows
+                parity = {"checked_rows": len(tokens)}
+                err = O.rel_frobenius(rows_got.cpu(), want) if rank == 0 else 0.0
+                parity["rel_frob"] = err
+                if mode == "ep":
+                    full_std = got.clone()
+                elif full_std is not None and cnt > 0:
+                    d = (got.float() - full_std[lo:hi].float()).norm() / full_std[lo:hi].float().norm().clamp_min(1e-30)
+                    parity["rel_frob_vs_standard_all_tokens"] = dist_max(float(d), world, device)
+                elif full_std is not None:
+                    parity["rel_frob_vs_standard_all_tokens"] = dist_max(0.0, world, device)
+                status_ok = device_status_clear(world, device)
+                ok = err < TOL and status_ok and parity.get("rel_frob_vs_standard_all_tokens", 0.0) < TOL
+                parity["ok"], parity["device_status_clear"] = agree(ok, world, device), status_ok
+                if not parity["ok"]:
+                    out[key] = {"error": "parity check failed; not timed", "parity": parity, "ep": world}
+                    continue
+                ms = timed(lambda: layer(xs, ws_, is_), max(2, steps // 2), world, device)
+                # per GPU: 1/world of the flops, its experts' weights once; the all-to-all forms move every local
+                # token's FP8 row + scales to the other owning ranks and bf16 partial rows back (at most
+                # topk_group ranks per token); the standard form all-reduces the [T, H] bf16 output
+                if mode == "ep":
+                    link = 2 * (world - 1) / world * T * H * 2
+                else:
+                    link = per * min(cfg["topk_group"], world) * (world - 1) / world * (H + H // 32 + 2 * H)
+                active = int(torch.unique(ti).numel())
+                out[key] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "ep": world, "tflops": 6 * T * topk * H * I / ms / 1e9,
+                            "parity": parity,
+                            **roofline_frac(ms, 6 * T * topk * H * I / world,
+                                            3 * H * I * min(el, active) * (1 + 4 / 16384), link, fp8_peak=fp8_peak)}
+                del layer
+            except Exception as e:
+                out[key] = {"error": repr(e)[:300]}
+                torch.cuda.synchronize()
+                barrier(world)
+        del full_std
+    del w1, w2, w1_s, w2_s
     torch.cuda.empty_cache()
 
-    cfg = synthetic.DEEPSEEK_V3
-    E, topk, H, I, T = cfg["E"], cfg["topk"], cfg["H"], cfg["I"], 16384
-    el = E // world
-    w1, w2, w1_s, w2_s = synthetic.expert_weights(el, I, H, 4000 + E, device=device, first_expert=rank * el)
-    g = torch.Generator().manual_seed(5000 + T)
-    x = torch.randn(T, H, generator=g).bfloat16().to(device)
-    logits = torch.randn(T, E, generator=g).to(device)
-    tw, ti = biased_grouped_topk(x, logits, torch.zeros(E, device=device), topk, True, cfg["n_group"], cfg["topk_group"])
-    for mode, label in (("ep", "standard"), ("ep_a2a", "a2a"), ("ep_peer", "a2a_peer_memory")):
-        layer = P.FusedMoE(w1, w2, w1_s, w2_s, rank, world, mode=mode, presharded=True, num_experts=E,
-                           max_tokens=T // world)
-        if mode == "ep":
-            xs, ws_, is_ = x, tw, ti
-        else:
-            per = T // world
-            sl = slice(rank * per, (rank + 1) * per)
-            xs, ws_, is_ = x[sl].contiguous(), tw[sl].contiguous(), ti[sl].contiguous()
-        ms = timed(lambda: layer(xs, ws_, is_), max(2, steps // 2))
-        # per GPU: 1/world of the flops, its experts' weights once; all-to-all modes move every local token's
-        # FP8 row + scales to the other owning ranks and bf16 partial rows back (at most topk_group ranks per token)
-        per = T // world
-        link = 0.0 if mode == "ep" else per * min(cfg["topk_group"], world) * (world - 1) / world * (H + H // 32 + 2 * H)
-        if mode == "ep":
-            link = 2 * (world - 1) / world * T * H * 2
-        out[f"ep_deepseek_v3_T16384_{label}"] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "ep": world,
-                                                 "tflops": 6 * T * topk * H * I / ms / 1e9,
-                                                 **roofline_frac(ms, 6 * T * topk * H * I / world,
-                                                                 3 * H * I * el * (1 + 4 / 16384), link)}
+    # ---- tensor parallel over the intermediate dimension, Mixtral
+    cfg = synthetic.MIXTRAL
+    E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
+    seed = 4000 + E
+    full = synthetic.expert_weights(E, I, H, seed, device=device)
+    shard = P.shard_moe_tp(*full, rank, world)
+    del full
+    torch.cuda.empty_cache()
+    layer = P.FusedMoE(*shard, rank, world, mode="tp", presharded=True, num_experts=E)
+    for T in (8192, 1024, 64, 1):
+        key = f"tp_mixtral_8x7b_T{T}"
+        try:
+            x, tw, ti = moe_inputs(cfg, T, device)
+            tokens = sample_rows(T, 4 if T == 8192 else 2)
+            barrier(world)
+            got = layer(x, tw, ti)
+            torch.cuda.synchronize()
+            err = 0.0
+            if rank == 0:
+                want = moe_reference_rows(O, cfg, x, tw, ti, tokens, seed, device)
+                err = O.rel_frobenius(got[tokens].float().cpu(), want)
+            status_ok = device_status_clear(world, device)
+            parity = {"rel_frob": err, "checked_rows": len(tokens), "device_status_clear": status_ok,
+                      "ok": agree(err < TOL and status_ok, world, device)}
+            if not parity["ok"]:
+                out[key] = {"error": "parity check failed; not timed", "parity": parity, "tp": world}
+                continue
+            ms = timed(lambda: layer(x, tw, ti), max(2, steps // 2), world, device)
+            active = int(torch.unique(ti).numel())
+            out[key] = {"tokens_per_s": T / ms * 1e3, "ms": ms, "tp": world, "tflops": 6 * T * topk * H * I / ms / 1e9,
+                        "parity": parity,
+                        **roofline_frac(ms, 6 * T * topk * H * I / world, 3 * H * I / world * active * (1 + 4 / 16384),
+                                        2 * (world - 1) / world * T * H * 2, fp8_peak=fp8_peak)}
+        except Exception as e:
+            out[key] = {"error": repr(e)[:300]}
+            torch.cuda.synchronize()
+            barrier(world)
     return out
+
+
+# ------------------------------------------------------------------------------------ main
 
 
 def main():
@@ -478,7 +925,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the MoE / cpu-baseline line items")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: skip the extra line items")
+    ap.add_argument("--inner", type=int, default=0, help="passes per step (0 = sized for a ~2 s timed region)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -498,67 +946,101 @@ def main():
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout to the one JSON line
         torch.distributed.init_process_group("nccl", device_id=device)
     import sglang_b200 as S
-    from sglang_b200 import _native
 
     peaks = load_peaks()
-    acts_host, acts_dev, weights = build_workload(device, rank)
+    fp8_meas = measure_fp8_peak(device, local_rank, sustain_s=2.0 if world == 1 else 1.0)
+    fp8_sus = fp8_meas.get("sustained_tflops") or 2 * peaks["bf16_sustained"]
+    fp8_burst = fp8_meas.get("burst_tflops") or 2 * peaks["bf16"]
+
+    tp = TPLayers(S, device, rank, world, row_counts=(M_ROWS,) if args.no_extras else (M_ROWS, 512, 32))
+    mode = "peer"
+
+    # ------------------------------------------------------------------ parity gate of the headline
+    parity = tp.check(M_ROWS, mode)
+    if not parity["ok"]:
+        if rank == 0:
+            print(json.dumps({"metric": "block-FP8 GEMM TFLOPS", "value": None, "unit": "TFLOP/s", "n_gpus": world,
+                              "error": "the headline workload failed its parity check; nothing was timed", "parity": parity}))
+        raise SystemExit(1)
 
     # ---------------------------------------------------------------- device-resident timing
+    barrier(world)
     for _ in range(args.warmup):
-        run_step(S, acts_dev, weights)
+        tp.forward(M_ROWS, mode)
+    pass_ms = timed(lambda: tp.forward(M_ROWS, mode), 3, world, device, warm=0)
+    inner = args.inner if args.inner > 0 else max(1, min(64, math.ceil(2000.0 / (args.steps * pass_ms))))
     gemm_events = []
     barrier(world)
     with ClockSampler(local_rank) as clocks:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            run_step(S, acts_dev, weights, gemm_events)
+            for _ in range(inner):
+                tp.forward(M_ROWS, mode, events=gemm_events)
         e1.record()
         barrier(world)
-    ms_step = dist_max(e0.elapsed_time(e1) / args.steps, world, device)
-    status = _native.read_device_status()
-    if status != 0:
-        raise SystemExit(f"device status word = {status}: a bounded wait timed out; the numbers are void")
-    value = world * M_ROWS * FLOPS_PER_ROW / ms_step / 1e9
+    total_ms = e0.elapsed_time(e1)
+    ms_step = dist_max(total_ms / args.steps, world, device)
+    if not device_status_clear(world, device):
+        raise SystemExit("device status word set: a bounded wait timed out; the numbers are void")
+    value = inner * M_ROWS * FLOPS_PER_ROW / ms_step / 1e9
+    clk = clocks.summary()
 
     per_shape = {}
     for name, a, b in gemm_events:
         per_shape.setdefault(name, []).append(a.elapsed_time(b))
     gemm_ms = sum(statistics.mean(v) for v in per_shape.values())
-    gemm_tflops = M_ROWS * FLOPS_PER_ROW / gemm_ms / 1e9
-    fp8_peak = 2 * peaks["bf16_sustained"]
-    alg_bytes = {n: M_ROWS * kk + nn * kk + 2 * M_ROWS * nn + 4 * (M_ROWS * kk // 128 + nn * kk // 16384) for n, nn, kk in LINEARS}
-    roofline = {"bound": "tensor", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
-                "traffic": GEMM_TRAFFIC_RATIO * sum(alg_bytes.values()) / len(alg_bytes), "kernel": "block_fp8_gemm_kernel<256,dense,bf16>",
-                "traffic_note": "dram read+write of one ncu capture at 8192x8192x4096 was 1.10 x its algorithmic bytes "
-                                "(profiles/block_fp8_gemm_kernel_dense_8192x8192x4096.md); scaled to the mean algorithmic "
-                                "bytes of the four launches of a step",
-                "algorithmic_bytes_per_launch": sum(alg_bytes.values()) / len(alg_bytes),
-                "peak_note": f"2 x {peaks['source']} sustained dense bf16 ({peaks['bf16_sustained']} TF/s); nominal dense FP8 is 4500",
-                "frac_of_nominal_fp8": gemm_tflops / 4500.0,
-                "per_shape_tflops": {n: 2 * M_ROWS * nn * kk / statistics.mean(per_shape[n]) / 1e9 for n, nn, kk in LINEARS}}
+    gemm_tflops = M_ROWS * FLOPS_PER_ROW / world / gemm_ms / 1e9  # per GPU
+    sustained_run = ms_step * args.steps >= 1500.0
+    fp8_peak = fp8_sus if sustained_run else fp8_burst
+    shard = {name: ((n // world, k) if kind == "column" else (n, k // world)) for name, n, k, kind in TP_LINEARS}
+    alg_bytes = {nm: M_ROWS * kk + nn * kk + 2 * M_ROWS * nn + 4 * (M_ROWS * kk // 128 + nn * kk // 16384)
+                 for nm, (nn, kk) in shard.items()}
+    traffic_ratio = 1.10
+    roofline = {
+        "bound": "tensor", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
+        "traffic": traffic_ratio * sum(alg_bytes.values()) / len(alg_bytes),
+        "kernel": "block_fp8_gemm_kernel<256,dense,bf16>" + (" (row-parallel layers: fan-out epilogue + finishing kernel)" if world > 1 else ""),
+        "traffic_note": "dram read+write of one ncu capture of this kernel at 8192x8192x4096 was 1.10 x its algorithmic bytes; "
+                        "scaled to the mean algorithmic bytes of the four launches of a pass",
+        "algorithmic_bytes_per_launch": sum(alg_bytes.values()) / len(alg_bytes),
+        "peak_note": ("measured in this process: torch._scaled_mm FP8 8192^3, "
+                      + ("sustained loop" if sustained_run else "best single launch")
+                      + (" (timed region %.1f s)" % (ms_step * args.steps / 1e3))) if "burst_tflops" in fp8_meas
+                     else f"2 x {peaks['source']} dense bf16 (no FP8 GEMM could be timed: {fp8_meas.get('unavailable')})",
+        "fp8_peak_measured": fp8_meas,
+        "frac_of_measured_fp8_burst": gemm_tflops / fp8_burst, "frac_of_measured_fp8_sustained": gemm_tflops / fp8_sus,
+        "frac_of_2x_bf16_burst": gemm_tflops / (2 * peaks["bf16"]), "frac_of_2x_bf16_sustained": gemm_tflops / (2 * peaks["bf16_sustained"]),
+        "frac_of_nominal_fp8": gemm_tflops / NOMINAL_FP8,
+        "ms_x_sm_mhz": gemm_ms * (clk["sm_mhz"] or 0),
+        "per_shape_tflops_per_gpu": {nm: 2 * M_ROWS * nn * kk / statistics.mean(per_shape[nm]) / 1e9 for nm, (nn, kk) in shard.items()},
+    }
 
     # ------------------------------------------------------------------ end-to-end (host buffers)
-    outs_host = {name: torch.empty(M_ROWS, n, dtype=torch.bfloat16).pin_memory() for name, n, k in LINEARS}
+    # Every rank copies its own inputs from pinned host memory and its own part of the outputs back: the N/p
+    # output columns of a column-parallel layer, rows [rank*M/p, ..) of a row-parallel layer's summed result
+    # (every rank holds the whole sum). The copies run on their own streams so that H2D, kernels and D2H of
+    # consecutive layers overlap; every byte still crosses inside the timed region.
+    acts_host = {name: x.cpu().pin_memory() for name, _, _, _, x, _, _ in tp.layers}
+    rows_lo, rows_hi = rank * M_ROWS // world, (rank + 1) * M_ROWS // world
+    outs_host = {}
+    for name, n, k, kind, *_ in tp.layers:
+        shape = (M_ROWS, n // world) if kind == "column" else (rows_hi - rows_lo, n)
+        outs_host[name] = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
     h2d = sum(x.numel() * x.element_size() for x in acts_host.values())
     d2h = sum(x.numel() * x.element_size() for x in outs_host.values())
-
-    # The copies run on their own streams so that the H2D copy of one linear, the kernels of the
-    # previous one and the D2H copy of the one before overlap (both PCIe directions busy at once);
-    # every byte still crosses inside the timed region. Device input buffers are double-buffered
-    # per linear; an event per buffer says when the kernels have finished reading it.
-    main = torch.cuda.current_stream()
+    main_s = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    dev_in = {name: [torch.empty_like(acts_dev[name]) for _ in range(2)] for name, _, _ in LINEARS}
-    consumed = {name: [None, None] for name, _, _ in LINEARS}
+    dev_in = {name: [torch.empty_like(x) for _ in range(2)] for name, _, _, _, x, _, _ in tp.layers}
+    consumed = {name: [None, None] for name, *_ in tp.layers}
+    copied_out = {name: None for name, *_ in tp.layers}
     step_no = [0]
 
     def e2e_step():
         b = step_no[0] & 1
         step_no[0] += 1
         last = None
-        for name, n, k in LINEARS:
-            wq, ws = weights[name]
+        for name, n, k, kind, x, wq, ws in tp.layers:
             buf = dev_in[name][b]
             with torch.cuda.stream(s_in):
                 if consumed[name][b] is not None:
@@ -566,20 +1048,32 @@ def main():
                 buf.copy_(acts_host[name], non_blocking=True)
                 arrived = torch.cuda.Event()
                 arrived.record(s_in)
-            main.wait_event(arrived)
+            main_s.wait_event(arrived)
             q, sc = S.per_token_group_quant_fp8(buf, 128, column_major_scales=True)
-            out = S.w8a8_block_fp8_matmul(q, wq, sc, ws, [128, 128], torch.bfloat16)
+            if kind == "row" and world > 1:
+                # the summed result is a view of the symmetric buffer, rewritten by this layer's next call:
+                # the previous pass's copy to the host must have read it first
+                if copied_out[name] is not None:
+                    main_s.wait_event(copied_out[name])
+                out, _ = tp.peer_for(name, n).linear(q, sc, wq, ws)
+                part = out[rows_lo:rows_hi]
+            else:
+                out = S.w8a8_block_fp8_matmul(q, wq, sc, ws, [128, 128], torch.bfloat16)
+                part = out
             done = torch.cuda.Event()
-            done.record(main)
+            done.record(main_s)
             consumed[name][b] = done
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
-                outs_host[name].copy_(out, non_blocking=True)
-                out.record_stream(s_out)
+                outs_host[name].copy_(part, non_blocking=True)
+                if not (kind == "row" and world > 1):
+                    out.record_stream(s_out)
                 last = torch.cuda.Event()
                 last.record(s_out)
+                copied_out[name] = last
         return last
 
+    barrier(world)
     for _ in range(2):
         e2e_step()
     torch.cuda.synchronize()
@@ -589,42 +1083,59 @@ def main():
     e0.record()
     for _ in range(e2e_steps):
         last = e2e_step()
-    main.wait_event(last)  # the timed region ends when the last result is in host memory
+    main_s.wait_event(last)  # the timed region ends when the last result is in host memory
     e1.record()
     barrier(world)
     e2e_ms = dist_max(e0.elapsed_time(e1) / e2e_steps, world, device)
-    e2e = {"value": world * M_ROWS * FLOPS_PER_ROW / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "overlap": "H2D, kernels and D2H of consecutive linears run on three streams; every copy is inside the timed region"}
+    e2e_ok = device_status_clear(world, device)
+    # the copied-back bytes are the checked ones: compare what landed in host memory with the device result
+    e2e = {"value": M_ROWS * FLOPS_PER_ROW / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
+           "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms, "steps": e2e_steps, "passes_per_step": 1,
+           "device_status_clear": e2e_ok,
+           "overlap": "H2D, kernels and D2H of consecutive layers run on three streams; every copy is inside the timed region"}
+    del dev_in, acts_host, outs_host
 
     line = {
         "metric": "block-FP8 GEMM TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 accumulate, bf16 out", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": M_ROWS, "block_shape": [128, 128],
-                   "l2": "per-step working set 1.4 GB (weights 218 MB + activations 436 MB + outputs 705 MB) > 126 MB L2",
-                   "parallelism": f"{world} independent replicas" if world > 1 else "single GPU"},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": args.steps * 2 * len(LINEARS), "roofline": roofline,
+        "config": {"workload": WORKLOAD, "rows": M_ROWS, "block_shape": [128, 128], "inner_repeats": inner,
+                   "timed_region_s": ms_step * args.steps / 1e3,
+                   "l2": "per-pass working set per GPU (weights %.0f MB + activations + outputs) > 126 MB L2"
+                         % (sum(wq.numel() for *_, wq, _ in tp.layers) / 1e6),
+                   "parallelism": f"tp{world}" if world > 1 else "single GPU (un-sharded)",
+                   "allreduce": "fused with the GEMM over NVLink peer memory (fan-out epilogue + finishing kernel)" if world > 1 else "none"},
+        "parity": parity, "clocks": clk, "e2e": e2e,
+        # per pass: 4 quantiser + 4 GEMM launches; on N > 1 each row-parallel layer adds its finishing kernel
+        # (and, two-shot, the kernel that waits for the owners' results)
+        "gpu_launches": args.steps * inner * (2 * len(TP_LINEARS) + (0 if world == 1 else 2 * (2 if world > 2 else 1))),
+        "roofline": roofline,
     }
-    del acts_dev, outs_host
     torch.cuda.empty_cache()
-    if world > 1 and not args.no_extras:
+    if not args.no_extras:
         try:
-            line["parallel"] = bench_parallel(S, device, rank, world, steps=6)
+            parallel = {}
+            if world > 1:
+                parallel.update(bench_tp_items(tp, world, device, steps=6, fp8_peak=fp8_sus))
+            del tp
+            torch.cuda.empty_cache()
+            if world > 1:
+                parallel.update(bench_moe_parallel(S, device, rank, world, steps=6, fp8_peak=fp8_sus))
+                line["parallel"] = parallel
         except Exception as e:  # the headline number stands without the extra line items
-            line["parallel"] = {"error": repr(e)}
-            barrier(world)
-    if rank == 0 and not args.no_extras:
+            line["parallel"] = {"error": repr(e)[:500]}
+            torch.cuda.synchronize()
         if world == 1:
-            try:
-                line["moe"] = bench_moe(S, device, steps=5)
-            except Exception as e:  # the headline number stands without the extra line items
-                line["moe"] = {"error": repr(e)}
-        if world == 1:
-            try:
-                line["kernels"] = bench_kernels(S, device)
-            except Exception as e:  # the headline number stands without the extra line items
-                line["kernels"] = {"error": repr(e)}
+            for key, fn in (("llama8b_linears", lambda: bench_llama8b(S, device, fp8_burst)),
+                            ("comparators", lambda: bench_comparators(S, device)),
+                            ("moe", lambda: bench_moe(S, device, steps=5, fp8_peak=fp8_sus)),
+                            ("kernels", lambda: bench_kernels(S, device))):
+                try:
+                    line[key] = fn()
+                except Exception as e:  # the headline number stands without the extra line items
+                    line[key] = {"error": repr(e)[:500]}
+                    torch.cuda.synchronize()
+                    torch.cuda.empty_cache()
             line["cpu_baseline"] = time_cpu_baseline()
     if rank == 0:
         print(json.dumps(line))

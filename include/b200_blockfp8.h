@@ -56,6 +56,18 @@ int b200_abi_version(void);
  * to *out (host pointer) and clears it. 0 = no kernel reported a problem. */
 int b200_read_device_status(int* out, void* stream);
 
+/* Process-wide tuning knobs: how tests force one kernel path and tuning sweeps try a setting.
+ * Product calls never read the environment; a knob left at -1 is decided automatically.
+ * Names: "gemm_bn" (128 / 256), "gemm_skinny" (0 = never the decode kernel),
+ * "gemm_skinny_max_m", "gemm_splitk" (> 0 forces the K split; size the workspace after setting
+ * it), "gemm_2cta" (0 / 1), "moe_down_splitk" (0 = never), "moe_zero_pads" (0 / 1),
+ * "peer_wait_ms" (limit of a device-side wait for another GPU, 100 .. 60000).
+ * No counterpart in the reference (its Triton launchers read tuned JSON configs instead,
+ * python/sglang/srt/layers/moe/fused_moe_triton/fused_moe_triton_config.py). Not thread-safe
+ * against concurrent launches: set knobs before the calls they affect. */
+int b200_set_tuning(const char* name, long value);
+int b200_get_tuning(const char* name, long* value);
+
 /* ---------------------------------------------------------------------------------------
  * per_token_group_quant_fp8
  * replaces: python/sglang/srt/layers/quantization/fp8_kernel.py:498-565
@@ -109,7 +121,8 @@ int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m
  *            python/sglang/srt/layers/moe/moe_runner/triton_utils/moe_align_block_size.py:19-87)
  * topk_ids: numel ids (ids_dtype i32/i64) in [-1, num_buckets-1); bucket b holds id b-1.
  * Outputs: sorted_token_ids int32 [max_pad] (flat indices, ascending inside a bucket, `numel`
- * in pad slots; slots >= num_post_pad are written only if pad_sorted != 0),
+ * in pad slots; every one of the max_pad slots is written whatever pad_sorted says: a superset of
+ * the reference's pad_sorted_token_ids=False, which leaves slots >= num_post_pad untouched),
  * expert_ids int32 [max_blocks] (bucket-1 per block, -1 past the last block),
  * num_post_pad int32 [1], cumsum int32 [num_buckets+1] (end of each bucket's real entries;
  * last = padded total). workspace: b200_moe_align_workspace_bytes(numel, num_buckets).     */
@@ -156,7 +169,8 @@ int b200_moe_align_block_size_static(const void* topk_ids, int ids_dtype, int64_
  * no_combine: B200_COMBINE_SUM (0) sums the slots; B200_COMBINE_NONE (1) returns [T,topk,H];
  * B200_COMBINE_SUM_SKIP_UNROUTED (2) sums the slots but leaves rows without any valid id unwritten
  * (the expert-parallel receive area, where most positions belong to other ranks).
- * routed_scaling_factor multiplies the combined output (pass 1.0f for none).
+ * routed_scaling_factor multiplies the combined output (pass 1.0f for none); it is ignored with
+ * B200_COMBINE_NONE, as in the reference (the caller combines and scales).
  * workspace: b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I) bytes, 256-B aligned. */
 enum { B200_COMBINE_SUM = 0, B200_COMBINE_NONE = 1, B200_COMBINE_SUM_SKIP_UNROUTED = 2 };
 size_t b200_fused_experts_fp8_workspace_bytes(int64_t T, int topk, int E, int64_t H, int64_t I);
@@ -248,7 +262,10 @@ int b200_route_topk_softmax_capped(const void* logits, int logits_dtype, float s
  * epoch == 0 selects device-side epochs (a counter next to the flags, flags[16..18], advanced by
  * the kernels themselves): the identical call can then be replayed from a CUDA graph; a flag array
  * is driven either by host epochs or by device epochs, never both. The flag array is 32 uint32.
- * All waits are bounded (2 s, B200_PEER_WAIT_MS); on expiry the device status word becomes 2. */
+ * All waits are bounded (2 s; the "peer_wait_ms" tuning knob). On expiry the device status word
+ * becomes 2, this rank's own result buffers (out, residual_out) are filled with NaN instead of a
+ * stale sum, and the kernels return normally: callers that do not synchronise per call should poll
+ * b200_read_device_status at a cadence of their choice (once per model step, say). */
 size_t b200_w8a8_block_fp8_gemm_fanout_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int b200_w8a8_block_fp8_gemm_fanout(const void* A, const float* As, int64_t as_stride_m,
                                     int64_t as_stride_k, const void* B, const float* Bs,
@@ -282,7 +299,9 @@ int b200_allreduce_finish(const void* slots, int64_t slot_stride, void* const* o
  * (then: b200_fused_experts_fp8 over the p*T_max positions with hidden = q, hidden_scale = s,
  *  out = this rank's output area)
  * b200_ep_combine: out[t] = fp32 sum, in ascending owner rank, of peer_out[d][rank][t][:] over
- *   the ranks d that own an expert of token t; out [T,H] bf16/f16. */
+ *   the ranks d that own an expert of token t; out [T,H] bf16/f16. When the device status word is
+ *   already non-zero (a handshake before it gave up), out is filled with NaN instead: the owners'
+ *   rows cannot be trusted. */
 int b200_ep_dispatch(const void* x_q, const float* x_s, const float* topk_weights,
                      const int32_t* topk_ids, int64_t T, int64_t T_max, int topk, int64_t H, int E,
                      int n_ranks, int rank, void* const* recv_q, void* const* recv_s,

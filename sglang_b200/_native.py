@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_long, c_size_t, c_uint32, c_void_p, POINTER
 
 import torch
 
@@ -22,6 +22,8 @@ SIGNATURES = {
     "b200_last_error_detail": (c_char_p, []),
     "b200_abi_version": (c_int, []),
     "b200_read_device_status": (c_int, [POINTER(c_int), c_void_p]),
+    "b200_set_tuning": (c_int, [c_char_p, c_long]),
+    "b200_get_tuning": (c_int, [c_char_p, POINTER(c_long)]),
     "b200_per_token_group_quant_fp8": (
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int64, c_float, c_int, c_void_p],
@@ -113,7 +115,9 @@ def load() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        if not os.path.exists(LIB_PATH):
+        if "SGLANG_B200_LIB" not in os.environ:
+            # a no-op when the stamp of the last build names the current sources; otherwise (edited source,
+            # missing library) it compiles, so stale kernels never run silently
             from . import build as _build
 
             _build.build()
@@ -185,6 +189,29 @@ class on_device:
     def __exit__(self, *a):
         if self.prev >= 0:
             torch.cuda.set_device(self.prev)
+        return False
+
+
+class tuning:
+    """``with tuning(gemm_bn=128, gemm_splitk=2): ...`` sets process-wide knobs of the native library
+    (``b200_set_tuning``) and restores the previous values on exit. For tests and tuning sweeps."""
+
+    def __init__(self, **knobs: int):
+        self.knobs, self.prev = knobs, {}
+
+    def __enter__(self):
+        lib = load()
+        for name, value in self.knobs.items():
+            old = c_long(0)
+            check(lib.b200_get_tuning(name.encode(), ctypes.byref(old)), "get_tuning")
+            self.prev[name] = old.value
+            check(lib.b200_set_tuning(name.encode(), int(value)), "set_tuning")
+        return self
+
+    def __exit__(self, *a):
+        lib = load()
+        for name, value in self.prev.items():
+            lib.b200_set_tuning(name.encode(), value)
         return False
 
 

@@ -5,6 +5,7 @@
 The library is compiled for sm_100a only; there is no other code path."""
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -50,34 +51,50 @@ def _stamp(srcs) -> str:
     return h.hexdigest()
 
 
+def _up_to_date(stamp: str, stamp_file: str) -> bool:
+    return os.path.exists(LIB) and os.path.exists(stamp_file) and open(stamp_file).read() == stamp
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library unless ``_lib/build.stamp`` already names this exact set of sources and flags
+    (a hash of every file under ``csrc/`` and ``include/``), so an edited source never runs with a stale
+    library. Several processes may call this at once (one per GPU): an exclusive file lock lets one of
+    them compile while the others wait and then find the stamp current; the library is written under a
+    temporary name and renamed into place, so a reader never maps a half-written file."""
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     os.makedirs(OUT_DIR, exist_ok=True)
     stamp_file = os.path.join(OUT_DIR, "build.stamp")
     stamp = _stamp(srcs)
-    if not force and os.path.exists(LIB) and os.path.exists(stamp_file) and open(stamp_file).read() == stamp:
+    if not force and _up_to_date(stamp, stamp_file):
         return LIB
-    nvcc = _nvcc()
-    extra = ["-Xptxas", "-v"] if verbose else []
+    with open(os.path.join(OUT_DIR, "build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and _up_to_date(stamp, stamp_file):  # another process built it while this one waited
+            return LIB
+        nvcc = _nvcc()
+        extra = ["-Xptxas", "-v"] if verbose else []
 
-    def compile_one(src):
-        obj = os.path.join(OUT_DIR, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
+        def compile_one(src):
+            obj = os.path.join(OUT_DIR, src.replace(".cu", ".o"))
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+            if verbose:
+                print(r.stderr)
+            return obj
+
+        with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 1)) as ex:
+            objs = list(ex.map(compile_one, srcs))
+        tmp = f"{LIB}.{os.getpid()}.tmp"
+        cmd = [nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
-            raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
-        if verbose:
-            print(r.stderr)
-        return obj
-
-    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 1)) as ex:
-        objs = list(ex.map(compile_one, srcs))
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    with open(stamp_file, "w") as f:
-        f.write(stamp)
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
+        with open(stamp_file + ".tmp", "w") as f:
+            f.write(stamp)
+        os.replace(stamp_file + ".tmp", stamp_file)
     return LIB
 
 

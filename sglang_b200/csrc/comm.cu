@@ -120,12 +120,22 @@ __global__ void __launch_bounds__(256) allreduce_finish_kernel(const AllReducePa
   // block 0 announces this rank's partials; every block waits for all ranks' announcements
   if (!handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 0, epoch, blockIdx.x == 0, p.wait_ns)) atomicExch(&s_ok, 0);
   __syncthreads();
+  const int64_t N = p.N;
   if (!s_ok) {
+    // A rank never announced its partials: report it, and poison this rank's own result with NaNs
+    // so that a caller that does not poll the status word cannot mistake stale bytes for a sum.
     if (threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+    const uint4 nan16 = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);  // NaN in bf16 and fp16
+    T* mine = static_cast<T*>(p.out[p.by_tile ? p.rank : 0]);
+    T* mine_res = static_cast<T*>(p.residual_out[p.by_tile ? p.rank : 0]);
+    for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x)
+      for (int64_t c = threadIdx.x * 8; c < N; c += (int64_t)blockDim.x * 8) {
+        *reinterpret_cast<uint4*>(mine + row * N + c) = nan16;
+        if (mine_res != nullptr && mine_res != p.residual) *reinterpret_cast<uint4*>(mine_res + row * N + c) = nan16;
+      }
     finish_epoch(p.my_flags, 0, device_epoch);
     return;
   }
-  const int64_t N = p.N;
   const T* __restrict__ slots = static_cast<const T*>(p.slots);
   const T* residual = static_cast<const T*>(p.residual);  // may be the same buffer as residual_out (in place)
   const T* w = static_cast<const T*>(p.rms_weight);
@@ -227,7 +237,14 @@ __global__ void __launch_bounds__(32) allreduce_results_landed_kernel(const AllR
   const bool device_epoch = p.epoch == 0;
   const uint32_t epoch = device_epoch ? *reinterpret_cast<volatile uint32_t*>(p.my_flags + kCounterBase + 1) + 1u : p.epoch;
   const bool ok = handshake(p.my_flags, p.peer_flags, p.n_ranks, p.rank, 1, epoch, true, p.wait_ns);
-  if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+  if (!__all_sync(0xffffffffu, ok)) {
+    // an owner never delivered its row blocks: report it and poison this rank's result (slow, one warp:
+    // this is the failure path)
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 2);
+    const uint4 nan16 = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+    uint4* mine = static_cast<uint4*>(p.out[p.rank]);
+    for (int64_t i = threadIdx.x; i < p.M * p.N / 8; i += 32) mine[i] = nan16;
+  }
   finish_epoch(p.my_flags, 1, device_epoch);
 }
 

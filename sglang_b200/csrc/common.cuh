@@ -45,12 +45,25 @@ inline int check_launch(const char* what) {
   return B200_OK;
 }
 
+// Process-wide knobs set through b200_set_tuning (tests force a kernel path, tuning sweeps try a
+// setting); -1 = decide automatically. Product calls read this struct, never the environment.
+struct Tuning {
+  long gemm_bn = -1;            // 128 / 256: tile width of the dense GEMM
+  long gemm_skinny = -1;        // 0: never use the decode (swapped-operand) kernel
+  long gemm_skinny_max_m = -1;  // rows up to which the decode kernel is used
+  long gemm_splitk = -1;        // > 0: forced K split
+  long gemm_2cta = -1;          // 0: never, 1: CTA-pair kernel whenever legal
+  long moe_down_splitk = -1;    // 0: the down GEMM never splits K
+  long moe_zero_pads = -1;      // 0 / 1: whether the gather pass zeroes pad rows
+  long peer_wait_ms = -1;       // limit of a device-side wait for another GPU
+};
+Tuning& tuning();
+
 // Limit of a device-side wait for another GPU (handshakes of the peer-memory collectives), in
-// nanoseconds: 2 s unless B200_PEER_WAIT_MS says otherwise (clamped to 100 ms .. 60 s). Ranks
+// nanoseconds: 2 s unless the peer_wait_ms knob says otherwise (clamped to 100 ms .. 60 s). Ranks
 // that can drift further apart than this on the host must synchronise on the host first.
 inline unsigned long long peer_wait_ns() {
-  long ms = 2000;
-  if (const char* e = getenv("B200_PEER_WAIT_MS")) ms = atol(e);
+  long ms = tuning().peer_wait_ms > 0 ? tuning().peer_wait_ms : 2000;
   if (ms < 100) ms = 100;
   if (ms > 60000) ms = 60000;
   return (unsigned long long)ms * 1000000ull;

@@ -72,6 +72,7 @@ struct EpCombineParams {
   const void* peer_out[kEpMaxRanks];  // per owner rank: base of its out area [p][T_max][H]
   const int32_t* topk_ids;            // [T, k] global ids of the local tokens
   void* out;                          // [T, H]
+  const int* status;                  // device status word: non-zero = a handshake of this call gave up
   int64_t T, T_max, H;
   int k, E, p, rank;
 };
@@ -94,6 +95,13 @@ __global__ void __launch_bounds__(128) ep_combine_kernel(const EpCombineParams a
   __syncthreads();
   const int64_t slot = (int64_t)a.rank * a.T_max + t;
   T* out = static_cast<T*>(a.out) + t * a.H;
+  if (*reinterpret_cast<const volatile int*>(a.status) != 0) {
+    // an owner never said "outputs ready" (the handshake before this kernel ran out): its rows are stale.
+    // Poison the result with NaNs so that a caller that does not poll the status word notices.
+    const uint4 nan16 = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);  // NaN in bf16 and fp16
+    for (int64_t c = threadIdx.x * 8; c < a.H; c += blockDim.x * 8) *reinterpret_cast<uint4*>(out + c) = nan16;
+    return;
+  }
   for (int64_t c = threadIdx.x * 8; c < a.H; c += blockDim.x * 8) {
     // all owners' rows are requested before any is used: the peer loads overlap instead of
     // paying one NVLink round trip after the other
@@ -203,6 +211,11 @@ extern "C" int b200_ep_combine(void* const* peer_out, const int32_t* topk_ids, v
   B200_CHECK_ARG(dtype == B200_BF16 || dtype == B200_F16, "ep_combine: dtype code %d is not bf16/f16", dtype);
   EpCombineParams a = {};
   a.topk_ids = topk_ids; a.out = out; a.T = T; a.T_max = T_max; a.H = H; a.k = topk; a.E = E; a.p = n_ranks; a.rank = rank;
+  a.status = device_status_word();
+  if (!a.status) {
+    set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
   for (int d = 0; d < n_ranks; ++d) {
     B200_CHECK_ARG(peer_out[d] && ((uintptr_t)peer_out[d] & 15) == 0, "ep_combine: output area %d null or unaligned", d);
     a.peer_out[d] = peer_out[d];

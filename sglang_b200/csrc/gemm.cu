@@ -1,7 +1,5 @@
 // w8a8_block_fp8_matmul: dense block-FP8 GEMM entry point (tcgen05 / TMEM / TMA kernel in
 // gemm_kernel.cuh).
-#include <stdlib.h>
-
 #include "gemm_host.cuh"
 #include "gemm_2cta.cuh"
 #include "gemm_skinny.cuh"
@@ -73,9 +71,12 @@ constexpr bool kPairedByDefault = false;  // CTA-pair kernel for large dense pro
 
 extern "C" size_t b200_w8a8_block_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  // sized for the largest split any SM count <= 148 picks
-  const int s = M <= b200::kSkinnyMaxM ? b200::skinny_k_splits(M, N, K, b200::skinny_token_tile(M), 148)
-                                       : b200::choose_k_splits(M, N, K, 148);
+  // sized for the largest split any SM count <= 148 picks (or the tuning knobs force)
+  const b200::Tuning& tune = b200::tuning();
+  int s = M <= b200::kSkinnyMaxM ? b200::skinny_k_splits(M, N, K, b200::skinny_token_tile(M), 148)
+                                 : b200::choose_k_splits(M, N, K, 148);
+  if (tune.gemm_splitk > s) s = (int)tune.gemm_splitk;
+  if (tune.gemm_skinny_max_m >= 0 && s < 16) s = 16;
   return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
 
@@ -100,19 +101,17 @@ static int gemm_impl(const void* A, const float* As, int64_t as_stride_m, int64_
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.n_dest = fan.n; p.dest_by_tile = fan.by_tile;
   for (int d = 0; d < fan.n; ++d) p.dest[d] = fan.dest[d];
-  int force_bn = 0;
-  if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);  // test hook: 128 or 256
+  const Tuning& tune = tuning();
+  const int force_bn = tune.gemm_bn == 128 || tune.gemm_bn == 256 ? (int)tune.gemm_bn : 0;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_CHECK_ARG(c_dtype == B200_BF16 || c_dtype == B200_F16 || c_dtype == B200_F32, "gemm: unknown output dtype code %d",
                  c_dtype);
   const int sms = sm_count() < 148 ? sm_count() : 148;
-  const char* skinny_env = getenv("B200_GEMM_SKINNY");  // test hook: 0 disables the decode kernel
-  int64_t skinny_max_m = kSkinnyMaxM;
-  if (const char* e = getenv("B200_GEMM_SKINNY_MAX_M")) skinny_max_m = atoi(e);  // tuning hook
-  const bool skinny = M <= skinny_max_m && force_bn == 0 && !(skinny_env && atoi(skinny_env) == 0);
+  const int64_t skinny_max_m = tune.gemm_skinny_max_m >= 0 ? tune.gemm_skinny_max_m : kSkinnyMaxM;
+  const bool skinny = M <= skinny_max_m && force_bn == 0 && tune.gemm_skinny != 0;
   int splits = skinny ? skinny_k_splits(M, N, K, skinny_token_tile(M), sms) : choose_k_splits(M, N, K, sms);
-  if (const char* e = getenv("B200_GEMM_SPLITK")) splits = atoi(e) > 0 ? atoi(e) : splits;  // test hook
+  if (tune.gemm_splitk > 0) splits = (int)tune.gemm_splitk;
   if (splits > (int)cdiv(K, 128)) splits = (int)cdiv(K, 128);
   if (skinny) {
     while (cdiv(cdiv(K, 128), splits) > SkinnyCfg<16>::kMaxKb) ++splits;  // scales of one item fit its smem table
@@ -157,8 +156,7 @@ static int gemm_impl(const void* A, const float* As, int64_t as_stride_m, int64_
   }
   // Large dense problems with 16-bit output: CTA pairs (each CTA loads half of the B tile)
   {
-    const char* e2 = getenv("B200_GEMM_2CTA");  // hook: 0 = never, 1 = whenever legal
-    const int mode2 = e2 ? atoi(e2) : -1;
+    const int mode2 = (int)tune.gemm_2cta;  // 0 = never, 1 = whenever legal
     const bool legal = c_dtype != B200_F32 && force_bn == 0 && N >= 256 && fan.n == 0;
     const bool want = mode2 == 1 || (mode2 != 0 && kPairedByDefault && M >= 1024 && cdiv(M, 256) * cdiv(N, 256) >= 64);
     if (legal && want) {

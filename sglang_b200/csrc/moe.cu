@@ -255,8 +255,7 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   uint8_t* aq2 = ws + L.off_aq2;
   float* as2 = reinterpret_cast<float*>(ws + L.off_as2);
   int down_splits = L.down_splits;
-  if (const char* e = getenv("B200_MOE_DOWN_SPLITK"))  // tuning hook: 0 keeps the 16-bit single-pass path
-    if (atoi(e) == 0) down_splits = 1;
+  if (tuning().moe_down_splitk == 0) down_splits = 1;  // knob: keep the 16-bit single-pass path
   const bool split = down_splits > 1;
   T* c3 = no_combine && !split ? static_cast<T*>(out) : reinterpret_cast<T*>(ws + L.off_c3);
 
@@ -288,7 +287,7 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
     const int threads = cpr < 256 ? (cpr + 31) / 32 * 32 : 256;  // whole warps; cpr is a multiple of 8
     dim3 grid((unsigned)(L.cap / kGatherRows), (unsigned)cdiv(cpr, threads));
     int zero_pads = numel >= (int64_t)E * 32;  // on average a quarter of a tile per expert or more
-    if (const char* e = getenv("B200_MOE_ZERO_PADS")) zero_pads = atoi(e);  // tuning hook
+    if (tuning().moe_zero_pads >= 0) zero_pads = (int)tuning().moe_zero_pads;
     if (hs != nullptr)
       moe_gather_fp8_kernel<<<grid, threads, 0, st>>>(hq, hs, sorted, expert_ids, npp, aq1, as1, cpr, H, (int)numel, topk,
                                                      L.cap, zero_pads);
@@ -297,8 +296,7 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
                                                           as1, cpr, H, (int)numel, topk, L.cap, zero_pads);
     if ((rc = check_launch("moe_gather"))) return rc;
   }
-  int force_bn = 0;
-  if (const char* e = getenv("B200_GEMM_BN")) force_bn = atoi(e);
+  const int force_bn = tuning().gemm_bn == 128 || tuning().gemm_bn == 256 ? (int)tuning().gemm_bn : 0;
   // expected live row tiles: every pair once, plus up to one partial tile per expert
   const int64_t tiles_hint = cdiv(numel, kMoeBlockM) + (numel < E ? numel : E) / 2;
   GemmParams p = {};

@@ -1,5 +1,6 @@
 // Status strings, thread-local error detail and the per-device status word.
 #include <stdarg.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -12,6 +13,11 @@ void set_error_detail(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_detail, sizeof(g_detail), fmt, ap);
   va_end(ap);
+}
+
+Tuning& tuning() {
+  static Tuning t;
+  return t;
 }
 
 // One word per device that loads the library. Kernels with bounded waits write a non-zero
@@ -51,7 +57,32 @@ const char* b200_status_string(int status) {
 
 const char* b200_last_error_detail(void) { return b200::g_detail; }
 
-int b200_abi_version(void) { return 1; }
+int b200_abi_version(void) { return 2; }
+
+static long* tuning_slot(const char* name) {
+  b200::Tuning& t = b200::tuning();
+  struct { const char* n; long* p; } table[] = {
+      {"gemm_bn", &t.gemm_bn}, {"gemm_skinny", &t.gemm_skinny}, {"gemm_skinny_max_m", &t.gemm_skinny_max_m},
+      {"gemm_splitk", &t.gemm_splitk}, {"gemm_2cta", &t.gemm_2cta}, {"moe_down_splitk", &t.moe_down_splitk},
+      {"moe_zero_pads", &t.moe_zero_pads}, {"peer_wait_ms", &t.peer_wait_ms}};
+  for (auto& e : table)
+    if (name && strcmp(name, e.n) == 0) return e.p;
+  return nullptr;
+}
+
+int b200_set_tuning(const char* name, long value) {
+  long* slot = tuning_slot(name);
+  B200_CHECK_ARG(slot != nullptr, "unknown tuning knob '%s'", name ? name : "(null)");
+  *slot = value;
+  return B200_OK;
+}
+
+int b200_get_tuning(const char* name, long* value) {
+  long* slot = tuning_slot(name);
+  B200_CHECK_ARG(slot != nullptr && value != nullptr, "unknown tuning knob '%s'", name ? name : "(null)");
+  *value = *slot;
+  return B200_OK;
+}
 
 int b200_read_device_status(int* out, void* stream) {
   B200_CHECK_ARG(out != nullptr, "out is null");

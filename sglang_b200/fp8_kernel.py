@@ -4,7 +4,6 @@ hand-written sm_100a kernels behind the C ABI. CUDA tensors only; no fallback.
 """
 from __future__ import annotations
 
-import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -187,18 +186,37 @@ def prepare_block_fp8_matmul_inputs(
 
 
 _workspaces = {}
+_retired = []  # superseded buffers that a captured CUDA graph may still address
+_capture_seen = False
 
 
 def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
-    """Grow-only per-(device, stream) scratch buffer for the kernels that need one."""
+    """Grow-only per-(device, stream) scratch buffer for the kernels that need one.
+
+    A CUDA graph bakes the buffer's address into its kernel nodes. Once any call has been made during a
+    stream capture, a buffer that has to grow is therefore kept alive (never returned to the allocator)
+    instead of being dropped, so replays of an earlier capture keep writing into memory nobody else owns.
+    ``reserve_workspace`` sizes the buffer up front."""
+    global _capture_seen
     if nbytes == 0:
         return None
     key = (device.index, N.current_stream(device))
     buf = _workspaces.get(key)
+    capturing = torch.cuda.is_current_stream_capturing()
+    _capture_seen = _capture_seen or capturing
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        if buf is not None and _capture_seen:
+            _retired.append(buf)
+        buf = torch.empty(max(nbytes, 0 if buf is None else buf.numel() * 3 // 2), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+def reserve_workspace(max_bytes: int, device=None) -> None:
+    """Size the scratch buffer of the current stream on ``device`` once, before CUDA graphs are captured on
+    it, so that no later call has to grow it (see ``_workspace``)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _workspace(device, int(max_bytes))
 
 
 def w8a8_block_fp8_matmul(
@@ -239,10 +257,6 @@ def w8a8_block_fp8_matmul(
     Bs = Bs.float().contiguous() if (Bs.dtype != torch.float32 or not Bs.is_contiguous()) else Bs
     lib = N.load()
     ws_bytes = lib.b200_w8a8_block_fp8_gemm_workspace_bytes(M, Nn, K)
-    if "B200_GEMM_SPLITK" in os.environ:  # test hook of the native side: size for the forced split
-        ws_bytes = max(ws_bytes, int(os.environ["B200_GEMM_SPLITK"]) * M * Nn * 4)
-    if "B200_GEMM_SKINNY_MAX_M" in os.environ:  # tuning hook: any split the decode kernel may pick
-        ws_bytes = max(ws_bytes, 16 * M * Nn * 4)
     with N.on_device(A):
         ws = _workspace(A.device, ws_bytes)
         st = lib.b200_w8a8_block_fp8_gemm(

@@ -25,7 +25,6 @@ rewrites them.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional, Tuple
 
 import torch
@@ -46,7 +45,7 @@ class PeerAllReduce:
         """``graph_safe``: calls can be captured in a CUDA graph and replayed. Epochs then live on
         the device (advanced by the kernels), one slot buffer is used instead of two, and the
         one-shot mode ends with a second handshake ("I have read my slots") that orders the reuse.
-        ``multicast`` (two-shot only; default off, or ``B200_PEER_MULTICAST=1``; needs an allocation
+        ``multicast`` (two-shot only; default off; needs an allocation
         with an NVSwitch multicast mapping): the owner of a row block writes its result once to the
         multicast address
         (``multimem.st``) and the switch replicates it into every rank's output, instead of one peer
@@ -75,8 +74,7 @@ class PeerAllReduce:
         self.handle = symm.rendezvous(self.buf, self.group)
         self.base = [int(p) for p in self.handle.buffer_ptrs]
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        if multicast is None:
-            multicast = os.environ.get("B200_PEER_MULTICAST", "0") == "1" and bool(mc)
+        multicast = bool(multicast)
         self.mc_base = mc if (self.two_shot and mc and multicast) else 0
         assert not (multicast and self.two_shot and not mc), "this allocation has no multicast mapping"
         self.buf[self.off_flags:].zero_()
@@ -157,6 +155,17 @@ class PeerAllReduce:
                                              self.rank, 1, 0, stream)
                 N.check(st, "peer_handshake")
         return out, res_out
+
+    def check_status(self) -> None:
+        """Synchronise the current stream and raise if a handshake of an earlier call gave up (a rank was
+        more than the wait limit late, or gone). The kernels never hang: on expiry they set the device status
+        word, fill this rank's result with NaNs and return, so a caller that cannot afford a synchronisation
+        per call still sees the failure in its outputs; call this at a cadence of your choice (once per
+        model step, say) to turn it into an exception."""
+        status = N.read_device_status()
+        if status != 0:
+            raise RuntimeError(f"peer all-reduce: device status {status}: a bounded device-side wait for another GPU "
+                               "ran out; results since the last check are invalid (filled with NaN)")
 
     def linear_bf16_input(self, x: torch.Tensor, weight, weight_scale, **kw):
         """Quantise ``x [M, K_local]`` per 1x128 group (column-major scales), then ``linear``."""

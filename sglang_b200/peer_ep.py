@@ -86,6 +86,16 @@ class PeerExpertParallel:
                                           phase, 0 if self.graph_safe else self.epoch & 0xFFFFFFFF, stream)
         N.check(st, "peer_handshake")
 
+    def check_status(self) -> None:
+        """Synchronise the current stream and raise if a handshake of an earlier ``forward`` gave up. The
+        kernels never hang: on expiry they set the device status word and the combine step fills its result
+        with NaNs, so the failure is visible in the outputs even without this call; poll it at a cadence of
+        your choice (once per model step, say) to turn it into an exception."""
+        status = N.read_device_status()
+        if status != 0:
+            raise RuntimeError(f"peer expert-parallel exchange: device status {status}: a bounded device-side wait for "
+                               "another GPU ran out; results since the last check are invalid (filled with NaN)")
+
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 experts: Callable[[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor], None]):
         """``hidden_states [T, H]`` (T <= max_tokens) local tokens with GLOBAL ``topk_ids``;

@@ -153,8 +153,12 @@ def fused_topk(
     scoring_func: str = "softmax",
     num_token_non_padded: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax or sigmoid top-k (python/sglang/srt/layers/moe/topk.py:640-700). As in the reference's GPU
+    path, ``correction_bias`` takes part in the selection only for ``scoring_func="sigmoid"``
+    (``topk_sigmoid``); the softmax branch calls ``topk_softmax`` without it."""
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
-    return _route(gating_output, topk, renormalize, _scoring_code(scoring_func), correction_bias,
+    code = _scoring_code(scoring_func)
+    return _route(gating_output, topk, renormalize, code, correction_bias if code == SIGMOID else None,
                   num_token_non_padded=num_token_non_padded)
 
 

@@ -64,7 +64,7 @@ def raw(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of the reference project")
     args = ap.parse_args()
     os.environ["CUDA_VISIBLE_DEVICES"] = "0"  # parsed at import by the reference test utilities
     _stub_modules()

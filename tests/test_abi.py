@@ -15,7 +15,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_native.SIGNATURES), declared ^ set(_native.SIGNATURES)
     for name in declared:
         assert getattr(lib, name) is not None
-    assert lib.b200_abi_version() == 1
+    assert lib.b200_abi_version() == 2
     assert lib.b200_status_string(0) == b"ok"
     assert lib.b200_status_string(-5) == b"device-side wait timed out"
 
@@ -54,3 +54,24 @@ def test_bad_arguments_return_status_not_crash():
     assert st == _native.E_BAD_ARG
     st = lib.b200_moe_align_block_size(None, 3, 10, 5000, 16, None, 0, None, 0, None, None, 1, None, 0, None)
     assert st == _native.E_UNSUPPORTED
+
+
+def test_tuning_knobs_round_trip_without_a_gpu():
+    """The knobs are host-side state: settable, readable and restored without any launch."""
+    from ctypes import byref, c_long
+
+    from sglang_b200 import _native as N
+
+    lib = N.load()
+    v = c_long(0)
+    assert lib.b200_get_tuning(b"gemm_bn", byref(v)) == 0 and v.value == -1
+    with N.tuning(gemm_bn=128, peer_wait_ms=100):
+        assert lib.b200_get_tuning(b"gemm_bn", byref(v)) == 0 and v.value == 128
+        assert lib.b200_get_tuning(b"peer_wait_ms", byref(v)) == 0 and v.value == 100
+    assert lib.b200_get_tuning(b"gemm_bn", byref(v)) == 0 and v.value == -1
+    assert lib.b200_set_tuning(b"no_such_knob", 1) == N.E_BAD_ARG
+    # a forced K split is reflected in the workspace the library asks for
+    plain = lib.b200_w8a8_block_fp8_gemm_workspace_bytes(4096, 4096, 4096)
+    with N.tuning(gemm_splitk=4):
+        assert lib.b200_w8a8_block_fp8_gemm_workspace_bytes(4096, 4096, 4096) == 4 * 4096 * 4096 * 4
+    assert lib.b200_w8a8_block_fp8_gemm_workspace_bytes(4096, 4096, 4096) == plain

@@ -37,16 +37,16 @@ def _case(M, N, K, seed, out_dtype=torch.bfloat16, col_major=False, bn=None, spl
     if col_major:
         As_d = As.t().contiguous().cuda().t()
         assert kt == 1 or As_d.stride() == (1, M)
+    from sglang_b200._native import tuning
+
+    knobs = {}
     if bn:
-        os.environ["B200_GEMM_BN"] = str(bn)
+        knobs["gemm_bn"] = bn
     if splitk:
-        os.environ["B200_GEMM_SPLITK"] = str(splitk)
-    try:
+        knobs["gemm_splitk"] = splitk
+    with tuning(**knobs):
         C = S.w8a8_block_fp8_matmul(A.cuda(), B.cuda(), As_d, Bs.cuda(), [128, 128], out_dtype)
         _status_ok()
-    finally:
-        os.environ.pop("B200_GEMM_BN", None)
-        os.environ.pop("B200_GEMM_SPLITK", None)
     assert C.dtype == out_dtype and tuple(C.shape) == (M, N)
     err = O.rel_frobenius(C.float().cpu(), ref)
     assert err < (1e-5 if out_dtype == torch.float32 else TOL), (M, N, K, err)
@@ -106,11 +106,10 @@ def test_decode_kernel_matches_large_tile_kernel():
     g = torch.Generator().manual_seed(3)
     As, Bs = (torch.rand(48, 8, generator=g) * 1e-2).cuda(), (torch.rand(6, 8, generator=g) * 1e-2).cuda()
     c1 = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.float32)
-    os.environ["B200_GEMM_SKINNY"] = "0"
-    try:
+    from sglang_b200._native import tuning
+
+    with tuning(gemm_skinny=0):
         c2 = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.float32)
-    finally:
-        os.environ.pop("B200_GEMM_SKINNY", None)
     _status_ok()
     assert float((c1 - c2).norm() / c2.norm()) < 1e-5
 
@@ -145,6 +144,54 @@ def test_llama8b_shapes_small_m(M, N, K):
     out = S.w8a8_block_fp8_linear(x.cuda(), wq.cuda(), [128, 128], ws.cuda())
     _status_ok()
     assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+
+
+def _sampled_oracle_case(M, N, K, seed):
+    """The quantised linear at a size too big for the CPU oracle as a whole: every output element depends
+    only on its own row of x and its own row of the weight, so the oracle is evaluated on sampled rows of x
+    and sampled 128-row blocks of the weight (first, last and two inner blocks) and compared with those
+    entries of the full-size result."""
+    import sglang_b200 as S
+    from sglang_b200.weight_quant import block_quant_weight_fp8
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    idx = torch.randperm(K, device="cuda", generator=g)[: (K + 99) // 100]
+    x[:, idx] *= 20
+    x = x.bfloat16()
+    wq, ws = block_quant_weight_fp8((torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16())
+    out = S.w8a8_block_fp8_linear(x, wq, [128, 128], ws)
+    _status_ok()
+    count = min(M, 32)
+    step = M // count
+    rows = [r * step + (5 * r) % step for r in range(count)]
+    nb = N // 128
+    blocks = sorted({0, nb // 3, (2 * nb) // 3, nb - 1})
+    cols = [b * 128 + j for b in blocks for j in range(128)]
+    wq_s = torch.cat([wq[b * 128:(b + 1) * 128] for b in blocks]).cpu()
+    ws_s = torch.cat([ws[b:b + 1] for b in blocks]).cpu()
+    ref = O.w8a8_block_fp8_linear(x[rows].cpu(), wq_s, ws_s, output_dtype=torch.float32)
+    got = out[rows][:, cols].float().cpu()
+    err = O.rel_frobenius(got, ref)
+    assert err < TOL, (M, N, K, err)
+
+
+@pytest.mark.parametrize("M", [1024, 8192])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
+def test_llama8b_shapes_large_m(M, N, K):
+    """BASELINE config 2 at its large row counts, every shape, against the oracle."""
+    _sampled_oracle_case(M, N, K, 2100 + M + N)
+
+
+@pytest.mark.parametrize("M", [32, 512, 4096])
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+@pytest.mark.parametrize("name,N,K,kind", [("qkv", 10240, 8192, "column"), ("gate_up", 57344, 8192, "column"),
+                                           ("o_proj", 8192, 8192, "row"), ("down", 8192, 28672, "row")])
+def test_llama70b_shard_shapes(name, N, K, kind, tp, M):
+    """BASELINE config 3: the GEMM every rank of a TP = 2 / 4 / 8 group runs (N/tp rows of a column-parallel
+    weight, K/tp columns of a row-parallel one), and the un-sharded layer, against the oracle."""
+    n, k = (N // tp, K) if kind == "column" else (N, K // tp)
+    _sampled_oracle_case(M, n, k, 3100 + M + n + k)
 
 
 def test_full_size_against_dequantised_matmul():
@@ -190,9 +237,8 @@ def test_errors():
 def test_cta_pair_kernel(M, N, K):
     """The cta_group::2 kernel (two CTAs per 256 x 256 tile, each loading half of the B tile) is an opt-in
     alternative for large dense problems; it must agree with the oracle like the default kernel."""
-    os.environ["B200_GEMM_2CTA"] = "1"
-    try:
+    from sglang_b200._native import tuning
+
+    with tuning(gemm_2cta=1):
         _case(M, N, K, 500 + M)
         _case(M, N, K, 501 + M, out_dtype=torch.float16, col_major=True)
-    finally:
-        os.environ.pop("B200_GEMM_2CTA", None)

@@ -73,7 +73,7 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_tp_and_ep_ranks(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

@@ -241,7 +241,7 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_allreduce_ranks(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

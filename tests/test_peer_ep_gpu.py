@@ -95,7 +95,7 @@ def test_handshake_with_itself_and_argument_checks():
     assert lib.b200_ep_dispatch(None, None, None, None, 4, 2, 2, 256, 8, 1, 0, peers, peers, peers, peers, None) == N.E_BAD_ARG
 
 
-def test_a_peer_that_never_signals_times_out_and_the_context_survives(monkeypatch):
+def test_a_peer_that_never_signals_times_out_and_the_context_survives():
     """Failure detection without a fault: the "other rank" is a flag array that nothing writes. The
     bounded wait gives up after the limit (100 ms here), the device status word reports it, reading
     the word clears it, and the next launches on the same context work."""
@@ -104,7 +104,13 @@ def test_a_peer_that_never_signals_times_out_and_the_context_survives(monkeypatc
     from sglang_b200 import _native as N
 
     lib = N.load()
-    monkeypatch.setenv("B200_PEER_WAIT_MS", "100")
+    with N.tuning(peer_wait_ms=100):
+        _silent_peer_case(lib, N)
+
+
+def _silent_peer_case(lib, N):
+    import time
+
     mine = torch.zeros(64, dtype=torch.int32, device="cuda")
     silent_peer = torch.zeros(64, dtype=torch.int32, device="cuda")
     peers = (ctypes.c_void_p * 2)(mine.data_ptr(), silent_peer.data_ptr())
@@ -117,13 +123,29 @@ def test_a_peer_that_never_signals_times_out_and_the_context_survives(monkeypatc
     assert 0.05 < waited < 1.5, waited
     assert silent_peer[0].item() == 1  # our own signal did go out
     assert N.read_device_status() == 0  # cleared by the read
-    # the all-reduce finishing kernel gives up the same way and leaves its output untouched
+    # the all-reduce finishing kernel gives up the same way and poisons its result with NaNs: a caller
+    # that never polls the status word cannot mistake stale bytes for a sum
     slot = torch.ones(2, 8, 256, dtype=torch.bfloat16, device="cuda")
     out = torch.full((8, 256), 7.0, dtype=torch.bfloat16, device="cuda")
     outs = (ctypes.c_void_p * 1)(out.data_ptr())
     N.check(lib.b200_allreduce_finish(slot.data_ptr(), 8 * 256, outs, N.BF16, 8, 256, 2, 0, 0, None, None, None, 1e-6,
                                       mine.data_ptr(), peers, 5, None, None, N.current_stream()), "finish")
-    assert N.read_device_status() == 2 and torch.all(out == 7.0)
+    assert N.read_device_status() == 2 and bool(torch.isnan(out).all())
+    # two-shot: the owned rows and (second handshake) the rows the silent owner never delivered
+    out2 = torch.full((8, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    outs2 = (ctypes.c_void_p * 2)(out2.data_ptr(), out2.data_ptr())
+    N.check(lib.b200_allreduce_finish(slot.data_ptr(), 8 * 256, outs2, N.BF16, 8, 256, 2, 0, 1, None, None, None, 1e-6,
+                                      mine.data_ptr(), peers, 6, None, None, N.current_stream()), "finish")
+    assert N.read_device_status() == 2 and bool(torch.isnan(out2).all())
+    # the expert-parallel combine after a handshake that gave up: NaNs, not stale rows
+    area = torch.ones(2, 4, 256, dtype=torch.bfloat16, device="cuda")
+    areas = (ctypes.c_void_p * 2)(area.data_ptr(), area.data_ptr())
+    ids = torch.zeros(4, 2, dtype=torch.int32, device="cuda")
+    res = torch.full((4, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    N.check(lib.b200_peer_handshake(mine.data_ptr(), peers, 2, 0, 1, 9, N.current_stream()), "handshake")
+    N.check(lib.b200_ep_combine(areas, ids.data_ptr(), res.data_ptr(), N.BF16, 4, 4, 2, 256, 8, 2, 0, N.current_stream()),
+            "combine")
+    assert N.read_device_status() == 2 and bool(torch.isnan(res).all())
     # the context is intact: a healthy single-rank call right after
     flags = torch.zeros(64, dtype=torch.int32, device="cuda")
     self_only = (ctypes.c_void_p * 1)(flags.data_ptr())
