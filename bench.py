@@ -413,16 +413,24 @@ class TPLayers:
 
 
 # --------------------------------------------------------------------------- CPU baseline legs
+# The host arm runs the oracle (the reference's torch-native path: quantise the rows, dequantise the whole weight,
+# fp32 matmul per 128 x 128 block) on a bounded sample of the headline workload: the first R of the 4096 rows
+# against the complete un-sharded weights. The weight dequantisation the reference pays per call is then spread
+# over R rows instead of 4096, so R is made as large as the time budget allows and is stated in the line.
 
 
 def cpu_inputs(rows: int):
-    """The un-sharded layers for the host arm: same shapes and distributions, drawn and quantised on the CPU."""
+    """Rows of every layer's input and its complete weight, with the shapes and distributions of the GPU arm.
+    To keep the set-up short the weight is one seeded, block-quantised 1024-row slab repeated along N (the
+    values do not change what the host path computes per element)."""
     from sglang_b200 import synthetic
 
     acts, weights = {}, {}
     for i, (name, n, k, _) in enumerate(TP_LINEARS):
         acts[name] = synthetic.activation(rows, k, 2000 + 10 * i)
-        weights[name] = synthetic.weight(n, k, 2001 + 10 * i)
+        wq, ws = synthetic.weight(1024, k, 2001 + 10 * i)
+        reps = n // 1024
+        weights[name] = (wq.repeat(reps, 1), ws.repeat(reps, 1))
     return acts, weights
 
 
@@ -436,17 +444,26 @@ def cpu_linears(rows: int, threads: int, weights_cpu, acts_cpu):
         O.w8a8_block_fp8_linear(acts_cpu[name][:rows], wq, ws, output_dtype=torch.bfloat16)
 
 
-def time_cpu_baseline(budget_s: float = 15.0):
+def cpu_rows_for(target_s: float, threads: int, weights, acts, cap: int) -> int:
+    """Rows per pass so that a pass takes about ``target_s``: two probe passes give the fixed (dequantisation)
+    and the per-row cost."""
+    cpu_linears(32, threads, weights, acts)  # warm-up of the thread pool and allocator
+    t0 = time.perf_counter()
+    cpu_linears(32, threads, weights, acts)
+    t32 = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    cpu_linears(160, threads, weights, acts)
+    t160 = time.perf_counter() - t0
+    per_row = max((t160 - t32) / 128, 1e-5)
+    fixed = max(t32 - 32 * per_row, 0.0)
+    return int(max(32, min(cap, (target_s - fixed) / per_row))) // 32 * 32
+
+
+def time_cpu_baseline(budget_s: float = 14.0):
     """Oracle on the host cores on a bounded row sample sized to ~budget_s of CPU work."""
     threads = os.cpu_count() or 1
-    rows = 32
     acts, weights = cpu_inputs(1024)
-    t0 = time.perf_counter()
-    cpu_linears(rows, threads, weights, acts)
-    dt = time.perf_counter() - t0
-    # scale the sample towards the budget (the first pass doubles as warm-up)
-    rows = int(max(32, min(1024, rows * budget_s / max(dt, 1e-3) / 2)))
-    rows = rows // 32 * 32
+    rows = cpu_rows_for(budget_s / 2, threads, weights, acts, 1024)
     t0 = time.perf_counter()
     cpu_linears(rows, threads, weights, acts)
     dt = time.perf_counter() - t0
@@ -461,15 +478,10 @@ def run_reference(args, rank: int):
         return
     threads = os.cpu_count() or 1
     acts, weights = cpu_inputs(1024)
-    # Size the step from one probe pass: about 3 s of host work per step (less when many steps are asked for, so
-    # that the whole run stays near two minutes), at least 32 rows. Every pass dequantises the weights, as the
-    # reference's native path does per call; larger samples amortise that the way the full 4096 rows would.
-    cpu_linears(32, threads, weights, acts)
-    t1 = time.perf_counter()
-    cpu_linears(128, threads, weights, acts)
-    per_128 = time.perf_counter() - t1
-    target = min(3.0, 120.0 / max(1, args.steps + args.warmup))
-    rows = int(max(32, min(1024, 128 * target / max(per_128, 1e-3)))) // 32 * 32
+    # about 6 s of host work per step, less when many steps are asked for so that the whole run stays within a
+    # few minutes
+    target = min(6.0, 150.0 / max(1, args.steps + args.warmup))
+    rows = cpu_rows_for(target, threads, weights, acts, 1024)
     for _ in range(args.warmup):
         cpu_linears(rows, threads, weights, acts)
     t0 = time.perf_counter()
