@@ -115,6 +115,27 @@ int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m
                              size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * w8a8_block_fp8_linear at decode size: quantise + GEMM + split-K sum in ONE launch
+ * replaces: the composition of python/sglang/srt/layers/quantization/fp8_utils.py:814-834
+ *           (per_token_group_quant_fp8, then w8a8_block_fp8_matmul) for M <= 16 rows; the
+ *           reference chains its quantiser and GEMM as programmatic dependents instead
+ *           (sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:456-466)
+ * out[m,n] = sum_kb (q(x)[m,kb] . B[n,kb]) * xs[m,kb] * Bs[n/128,kb] with q / xs the 1x128 group
+ * quantisation of x (arithmetic variant 0, eps as given): the same bytes and scales the stand-alone
+ * quantiser produces, so the result equals quantise-then-GEMM up to the fp32 summation order.
+ * x [M,K] bf16/f16 row-major (M <= 16), B [N,K] e4m3, Bs fp32 [ceil(N/128), ceil(K/128)],
+ * out [M,N] in the dtype of x. K % 16 == 0, N % 8 == 0, N <= 524288.
+ * workspace: b200_w8a8_block_fp8_linear_decode_workspace_bytes(M,N,K) bytes (fp32 partials of the K
+ * splits). tickets: 4096 uint32 that are ZERO before the first call and belong to one stream (every
+ * call leaves them zero; calls that overlap on the GPU must not share them). Anything else:
+ * B200_E_UNSUPPORTED (callers fall back to the two-step path). */
+size_t b200_w8a8_block_fp8_linear_decode_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int b200_w8a8_block_fp8_linear_decode(const void* x, int x_dtype, const void* B, const float* Bs,
+                                      void* out, int64_t M, int64_t N, int64_t K, float eps,
+                                      void* workspace, size_t workspace_bytes, void* tickets,
+                                      void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * moe_align_block_size
  * replaces: torch.ops.sgl_kernel.moe_align_block_size
  *           (sgl-kernel/csrc/moe/moe_align_kernel.cu:317-383; wrapper
@@ -132,6 +153,27 @@ int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel
                               int64_t max_pad, int32_t* expert_ids, int64_t max_blocks,
                               int32_t* num_post_pad, int32_t* cumsum, int pad_sorted,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * w8a8_block_fp8_linear at decode size: quantise + GEMM + split-K sum in ONE launch
+ * replaces: the composition of python/sglang/srt/layers/quantization/fp8_utils.py:814-834
+ *           (per_token_group_quant_fp8, then w8a8_block_fp8_matmul) for M <= 16 rows; the
+ *           reference chains its quantiser and GEMM as programmatic dependents instead
+ *           (sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:456-466)
+ * out[m,n] = sum_kb (q(x)[m,kb] . B[n,kb]) * xs[m,kb] * Bs[n/128,kb] with q / xs the 1x128 group
+ * quantisation of x (arithmetic variant 0, eps as given): the same bytes and scales the stand-alone
+ * quantiser produces, so the result equals quantise-then-GEMM up to the fp32 summation order.
+ * x [M,K] bf16/f16 row-major (M <= 16), B [N,K] e4m3, Bs fp32 [ceil(N/128), ceil(K/128)],
+ * out [M,N] in the dtype of x. K % 16 == 0, N % 8 == 0, N <= 524288.
+ * workspace: b200_w8a8_block_fp8_linear_decode_workspace_bytes(M,N,K) bytes (fp32 partials of the K
+ * splits). tickets: 4096 uint32 that are ZERO before the first call and belong to one stream (every
+ * call leaves them zero; calls that overlap on the GPU must not share them). Anything else:
+ * B200_E_UNSUPPORTED (callers fall back to the two-step path). */
+size_t b200_w8a8_block_fp8_linear_decode_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int b200_w8a8_block_fp8_linear_decode(const void* x, int x_dtype, const void* B, const float* Bs,
+                                      void* out, int64_t M, int64_t N, int64_t K, float eps,
+                                      void* workspace, size_t workspace_bytes, void* tickets,
+                                      void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * moe_align_block_size without a workspace (no counterpart in the reference).

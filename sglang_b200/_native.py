@@ -38,6 +38,12 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
          c_void_p, c_size_t, c_void_p],
     ),
+    "b200_w8a8_block_fp8_linear_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "b200_w8a8_block_fp8_linear_decode": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t,
+         c_void_p, c_void_p],
+    ),
     "b200_moe_align_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "b200_moe_align_block_size": (
         c_int,
@@ -213,6 +219,12 @@ class tuning:
         for name, value in self.prev.items():
             lib.b200_set_tuning(name.encode(), value)
         return False
+
+
+def get_tuning(name: str) -> int:
+    v = c_long(0)
+    check(load().b200_get_tuning(name.encode(), ctypes.byref(v)), "get_tuning")
+    return v.value
 
 
 def read_device_status() -> int:

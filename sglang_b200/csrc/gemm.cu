@@ -3,6 +3,7 @@
 #include "gemm_host.cuh"
 #include "gemm_2cta.cuh"
 #include "gemm_skinny.cuh"
+#include "linear_decode.cuh"
 
 namespace b200 {
 
@@ -203,4 +204,50 @@ extern "C" int b200_w8a8_block_fp8_gemm_fanout(const void* A, const float* As, i
   for (int d = 0; d < n_dest; ++d) fan.dest[d] = dest[d];
   return gemm_impl(A, As, as_stride_m, as_stride_k, B, Bs, nullptr, c_dtype, M, N, K, workspace, workspace_bytes, stream,
                    fan);
+}
+
+extern "C" size_t b200_w8a8_block_fp8_linear_decode_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int s = b200::decode_linear_k_splits(N, K, 148);
+  return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
+}
+
+extern "C" int b200_w8a8_block_fp8_linear_decode(const void* x, int x_dtype, const void* B, const float* Bs, void* out,
+                                                 int64_t M, int64_t N, int64_t K, float eps, void* workspace,
+                                                 size_t workspace_bytes, void* tickets, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(M >= 0 && N >= 0 && K > 0, "linear_decode: bad shape");
+  if (M == 0 || N == 0) return B200_OK;
+  B200_UNSUPPORTED(M > DecodeLinearCfg::NT, "linear_decode: M=%lld rows (at most %d)", (long long)M, DecodeLinearCfg::NT);
+  B200_UNSUPPORTED(x_dtype != B200_BF16 && x_dtype != B200_F16, "linear_decode: 16-bit activations only (dtype code %d)", x_dtype);
+  B200_UNSUPPORTED(K % 16 != 0 || N % 8 != 0, "linear_decode: K=%lld must be a multiple of 16, N=%lld of 8", (long long)K,
+                   (long long)N);
+  B200_UNSUPPORTED(N > 4096 * 128, "linear_decode: N=%lld exceeds the ticket array (4096 weight tiles)", (long long)N);
+  B200_CHECK_ARG(x && B && Bs && out && tickets, "linear_decode: null pointer");
+  B200_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)B & 15) == 0, "linear_decode: x and B must be 16-byte aligned");
+  const int sms = sm_count() < 148 ? sm_count() : 148;
+  DecodeLinearParams p = {};
+  p.x = x; p.Bs = Bs; p.out = out; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.eps = eps;
+  p.num_kb = (int)cdiv(K, kBK);
+  p.n_tiles = (int)cdiv(N, 128);
+  p.k_splits = decode_linear_k_splits(N, K, sms);
+  p.kb_per_split = (int)cdiv(p.num_kb, p.k_splits);
+  p.k_splits = (int)cdiv(p.num_kb, p.kb_per_split);  // no empty split: every ticket is drawn
+  p.tickets = static_cast<unsigned*>(tickets);
+  if (p.k_splits > 1) {
+    const size_t need = (size_t)p.k_splits * (size_t)M * (size_t)N * sizeof(float);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) != 0) {
+      set_error_detail("linear_decode: split-K needs a 16-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
+      return B200_E_WORKSPACE;
+    }
+    p.partial = static_cast<float*>(workspace);
+  }
+  p.status = device_status_word();
+  if (!p.status) {
+    set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (x_dtype == B200_BF16) return launch_decode_linear<__nv_bfloat16, __nv_bfloat16>(B, p, st);
+  return launch_decode_linear<__half, __half>(B, p, st);
 }

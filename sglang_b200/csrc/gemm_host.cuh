@@ -3,6 +3,7 @@
 #pragma once
 
 #include <type_traits>
+#include <unordered_map>
 
 #include "gemm_kernel.cuh"
 
@@ -41,6 +42,29 @@ inline EncodeTiledFn encode_tiled_fn() {
 // out-of-range elements read as zero.
 inline int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t k_bytes, uint32_t box_rows,
                         const char* what) {
+  // Encoding a descriptor costs a driver call of a microsecond or two, as much as a decode kernel's whole
+  // launch: the descriptors of operands seen before (weights, reused activation buffers) are kept per
+  // thread, keyed by everything they are built from.
+  struct Key {
+    const void* base;
+    uint64_t rows, k_bytes;
+    uint32_t box_rows;
+    bool operator==(const Key& o) const {
+      return base == o.base && rows == o.rows && k_bytes == o.k_bytes && box_rows == o.box_rows;
+    }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return (size_t)((uintptr_t)k.base * 0x9E3779B97F4A7C15ull) ^ (size_t)(k.rows * 31 + k.k_bytes * 131 + k.box_rows);
+    }
+  };
+  static thread_local std::unordered_map<Key, CUtensorMap, Hash> cache;
+  const Key key{base, rows, k_bytes, box_rows};
+  auto hit = cache.find(key);
+  if (hit != cache.end()) {
+    *m = hit->second;
+    return B200_OK;
+  }
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) {
     set_error_detail("cuTensorMapEncodeTiled is not available from the driver");
@@ -58,6 +82,8 @@ inline int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_
                      (unsigned long long)rows, (unsigned long long)k_bytes, box_rows, (int)r);
     return B200_E_LAUNCH;
   }
+  if (cache.size() >= 4096) cache.clear();
+  cache.emplace(key, *m);
   return B200_OK;
 }
 

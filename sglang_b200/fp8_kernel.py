@@ -282,8 +282,46 @@ def w8a8_block_fp8_linear(
     assert input_scale is None
     input_2d = input.view(-1, input.shape[-1])
     output_shape = [*input.shape[:-1], weight.shape[0]]
-    q_input, x_scale = per_token_group_quant_fp8(input_2d, block_size[1], column_major_scales=True)
-    output = w8a8_block_fp8_matmul(q_input, weight, x_scale, weight_scale, block_size, output_dtype=input_2d.dtype)
+    output = _linear_decode_fused(input_2d, weight, block_size, weight_scale)
+    if output is None:
+        q_input, x_scale = per_token_group_quant_fp8(input_2d, block_size[1], column_major_scales=True)
+        output = w8a8_block_fp8_matmul(q_input, weight, x_scale, weight_scale, block_size, output_dtype=input_2d.dtype)
     if bias is not None:
         output += bias
     return output.to(dtype=input_2d.dtype).view(*output_shape)
+
+
+_tickets = {}
+DECODE_FUSED_MAX_M = 16
+
+
+def _linear_decode_fused(x: torch.Tensor, weight: torch.Tensor, block_size, weight_scale: torch.Tensor):
+    """At most 16 rows of 16-bit activations: quantiser, GEMM and split-K sum as ONE launch (every CTA
+    quantises the slice of ``x`` it needs; same bytes and scales as ``per_token_group_quant_fp8``). Returns
+    None when the shapes or dtypes are outside that kernel, and the caller takes the two-step path."""
+    M, K = x.shape
+    if not (0 < M <= DECODE_FUSED_MAX_M and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
+            and list(block_size) == [128, 128] and weight.dtype == fp8_dtype and weight.dim() == 2
+            and weight_scale.dtype == torch.float32 and weight_scale.is_contiguous() and x.is_contiguous()
+            and weight.is_contiguous() and K % 16 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] == K):
+        return None
+    if N.get_tuning("linear_decode_fused") == 0:
+        return None
+    Nn = weight.shape[0]
+    assert tuple(weight_scale.shape) == ((Nn + 127) // 128, (K + 127) // 128)
+    lib = N.load()
+    out = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
+    with N.on_device(x):
+        stream = N.current_stream()
+        key = (x.device.index, stream)
+        tickets = _tickets.get(key)
+        if tickets is None:  # zero once; every call leaves them zero
+            tickets = _tickets[key] = torch.zeros(4096, dtype=torch.int32, device=x.device)
+        ws_bytes = lib.b200_w8a8_block_fp8_linear_decode_workspace_bytes(M, Nn, K)
+        ws = _workspace(x.device, ws_bytes)
+        st = lib.b200_w8a8_block_fp8_linear_decode(
+            N.ptr(x), N.DTYPE_CODE[x.dtype], N.ptr(weight), N.ptr(weight_scale), N.ptr(out), M, Nn, K, 1e-10,
+            N.ptr(ws), ws_bytes, N.ptr(tickets), stream,
+        )
+    N.check(st, "w8a8_block_fp8_linear (decode)")
+    return out

@@ -194,6 +194,47 @@ def test_llama70b_shard_shapes(name, N, K, kind, tp, M):
     _sampled_oracle_case(M, n, k, 3100 + M + n + k)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 3, 16])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (6144, 4096), (28672, 4096), (4096, 14336), (512, 256), (1032, 384),
+                                 (128, 8192 + 128)])
+def test_one_launch_decode_linear(M, N, K, dtype):
+    """At most 16 rows: quantiser + GEMM + split-K sum run as one kernel. Against the oracle, against the
+    two-step path (same quantised bytes and scales, so only the fp32 summation order differs), and called
+    twice in a row (the split-K tickets must be left ready for the next call)."""
+    import sglang_b200 as S
+    from sglang_b200._native import tuning
+
+    x = make_activation(M, K, 2300 + M + K, dtype=dtype)
+    wq, ws = make_weight(N, K, 2301 + N)
+    ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
+    xd, wd, sd = x.cuda(), wq.cuda(), ws.cuda()
+    out = S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd)
+    out2 = S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd)
+    with tuning(linear_decode_fused=0):
+        two_step = S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd)
+    _status_ok()
+    assert out.dtype == dtype and tuple(out.shape) == (M, N)
+    assert torch.equal(out, out2)
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+    assert float((out.float() - two_step.float()).norm() / two_step.float().norm()) < 2e-3
+
+
+def test_one_launch_decode_linear_declines_other_shapes():
+    from sglang_b200 import _native as N
+
+    lib = N.load()
+    x = torch.zeros(17, 256, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(128, 256, device="cuda").to(torch.float8_e4m3fn)
+    s = torch.ones(1, 2, device="cuda")
+    out = torch.empty(17, 128, dtype=torch.bfloat16, device="cuda")
+    t = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    args = (N.ptr(w), N.ptr(s), N.ptr(out))
+    assert lib.b200_w8a8_block_fp8_linear_decode(N.ptr(x), N.BF16, *args, 17, 128, 256, 1e-10, None, 0, N.ptr(t), None) == N.E_UNSUPPORTED
+    assert lib.b200_w8a8_block_fp8_linear_decode(N.ptr(x), N.F32, *args, 4, 128, 256, 1e-10, None, 0, N.ptr(t), None) == N.E_UNSUPPORTED
+    assert lib.b200_w8a8_block_fp8_linear_decode(N.ptr(x), N.BF16, *args, 4, 128, 256, 1e-10, None, 0, None, None) == N.E_BAD_ARG
+
+
 def test_full_size_against_dequantised_matmul():
     """M=8192 x (N=6144, K=4096): too big for the CPU oracle in seconds, so compare with an
     fp32 matmul of the dequantised operands on the device (same math, other summation order)."""
