@@ -13,6 +13,7 @@
 #include <stdlib.h>
 
 #include "gemm_host.cuh"
+#include "moe_decode.cuh"
 
 namespace b200 {
 
@@ -205,9 +206,28 @@ struct MoeWorkspace {
   int64_t cap;  // rows of the expert-sorted layout (multiple of 128)
   int64_t cap_blocks;
   int down_splits;  // > 1: the down GEMM writes fp32 split-K partials instead of 16-bit rows
+  bool decode;      // few-token path: swapped-operand kernels, no align / gather pass
+  int decode_nt;    // its token tile (16, 32 or 64)
+  int decode_splits;  // K splits of its down stage
+  size_t off_act;   // its fp32 activation rows [numel][I] between the two stages
   bool quant_first;  // quantise the T input rows once, then gather FP8 rows (instead of quantising every pair)
   size_t off_sorted, off_expert, off_npp, off_cumsum, off_align, off_aq1, off_as1, off_aq2, off_as2, off_c3, off_xq, off_xs, total;
 };
+
+// K splits of the few-token down stage: about two work items (routed expert x 128-row weight tile x split)
+// per SM, at least as many as the scale table of one CTA requires.
+static int moe_decode_down_splits(int64_t numel, int E, int64_t H, int64_t I, int sms) {
+  const int64_t active = numel < E ? numel : E;
+  const int64_t items = active * (H / 128);
+  const int64_t num_kb = I / 128;
+  int64_t s = (2 * (int64_t)sms) / (items > 0 ? items : 1);
+  if (s > num_kb / 4) s = num_kb / 4;
+  const int64_t need = cdiv(num_kb, 64);
+  if (s < need) s = need;
+  if (s < 1) s = 1;
+  if (s > 16) s = 16 > need ? 16 : need;
+  return (int)s;
+}
 
 static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, int64_t I) {
   MoeWorkspace w = {};
@@ -233,8 +253,69 @@ static MoeWorkspace moe_workspace_layout(int64_t T, int topk, int E, int64_t H, 
   w.quant_first = topk >= 3;
   w.off_xq = take(w.quant_first ? (size_t)T * H : 0);
   w.off_xs = take(w.quant_first ? (size_t)T * (H / 128) * 4 : 0);
+  // a handful of tokens: the swapped-operand path (its buffers are taken in addition, so that the
+  // tuning knob can switch paths on the same workspace)
+  w.decode = T <= 64 && numel <= kDecodeMaxIds && E <= kDecodeMaxExperts && H <= 64 * 128 && H % 128 == 0 && I % 128 == 0;
+  w.decode_nt = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+  w.decode_splits = w.decode ? moe_decode_down_splits(numel, E, H, I, 148) : 1;
+  w.off_act = take(w.decode ? (size_t)numel * I * 4 : 0);
+  if (w.decode) {
+    const size_t need = (size_t)w.decode_splits * numel * H * 4;
+    const size_t have = w.down_splits > 1 ? (size_t)w.down_splits * numel * H * 4 : (size_t)numel * H * 2;
+    if (need > have) {  // the partials of the decode path share the c3 region: grow it
+      w.off_c3 = take(need);
+    }
+  }
   w.total = o;
   return w;
+}
+
+// Few-token path (see moe_decode.cuh): gate_up -> fp32 activation rows -> down -> slot / split sum.
+template <typename T>
+static int run_fused_experts_decode(const void* hidden, const float* hidden_scale, const void* w1, const void* w2,
+                                    const float* w1_scale, const float* w2_scale, const float* topk_weights,
+                                    const int32_t* topk_ids, void* out, int64_t T_tokens, int topk, int E, int64_t H,
+                                    int64_t I, int combine_mode, int weight_on_input, float routed_scale, uint8_t* ws,
+                                    const MoeWorkspace& L, cudaStream_t st) {
+  const int no_combine = combine_mode == B200_COMBINE_NONE;
+  const int skip_unrouted = combine_mode == B200_COMBINE_SUM_SKIP_UNROUTED;
+  const int64_t numel = T_tokens * topk;
+  const int max_active = (int)(numel < E ? numel : E);
+  MoeDecodeParams p = {};
+  p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.numel = (int)numel; p.topk = topk; p.E = E;
+  p.act = reinterpret_cast<float*>(ws + L.off_act);
+  p.partial = reinterpret_cast<float*>(ws + L.off_c3);
+  p.status = device_status_word();
+  if (!p.status) {
+    set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
+  // gate_up: K = H, 64 gate + 64 up rows per tile
+  p.x = hidden_scale ? nullptr : hidden;
+  p.x_q = hidden_scale ? static_cast<const uint8_t*>(hidden) : nullptr;
+  p.x_s = hidden_scale;
+  p.Bs = w1_scale; p.K = (int)H; p.num_kb = (int)(H / 128); p.n_out = (int)I; p.n_tiles = (int)(I / 64);
+  p.k_splits = 1; p.kb_per_split = p.num_kb; p.weight_on_input = weight_on_input; p.apply_weight = 0;
+  int rc;
+#define B200_MOE_DECODE(STAGE, W, ROWS)                                                             \
+  (L.decode_nt == 16   ? launch_moe_decode<16, STAGE, T>(W, ROWS, p, max_active, st)                \
+   : L.decode_nt == 32 ? launch_moe_decode<32, STAGE, T>(W, ROWS, p, max_active, st)                \
+                       : launch_moe_decode<64, STAGE, T>(W, ROWS, p, max_active, st))
+  if ((rc = B200_MOE_DECODE(1, w1, (int64_t)E * 2 * I))) return rc;
+  // down: K = I, 128 rows of w2 per tile, K split
+  p.x = nullptr; p.x_q = nullptr; p.x_s = nullptr;
+  p.Bs = w2_scale; p.K = (int)I; p.num_kb = (int)(I / 128); p.n_out = (int)H; p.n_tiles = (int)(H / 128);
+  p.kb_per_split = (int)cdiv(p.num_kb, L.decode_splits);
+  p.k_splits = (int)cdiv(p.num_kb, p.kb_per_split);
+  p.weight_on_input = 0; p.apply_weight = weight_on_input ? 0 : 1;
+  if ((rc = B200_MOE_DECODE(2, w2, (int64_t)E * H))) return rc;
+#undef B200_MOE_DECODE
+  const int64_t rows = no_combine ? numel : T_tokens;
+  const int64_t total = rows * (H / 8);
+  moe_sum_reduce_splits_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(
+      p.partial, topk_ids, static_cast<T*>(out), rows, no_combine ? 1 : topk, p.k_splits, numel * H, E, H,
+      no_combine ? 1.0f : routed_scale, skip_unrouted);
+  return check_launch("moe_sum_reduce_splits");
 }
 
 template <typename T>
@@ -254,6 +335,9 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   float* as1 = reinterpret_cast<float*>(ws + L.off_as1);
   uint8_t* aq2 = ws + L.off_aq2;
   float* as2 = reinterpret_cast<float*>(ws + L.off_as2);
+  if (L.decode && tuning().moe_decode != 0)
+    return run_fused_experts_decode<T>(hidden, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T_tokens,
+                                       topk, E, H, I, combine_mode, weight_on_input, routed_scale, ws, L, st);
   int down_splits = L.down_splits;
   if (tuning().moe_down_splitk == 0) down_splits = 1;  // knob: keep the 16-bit single-pass path
   const bool split = down_splits > 1;

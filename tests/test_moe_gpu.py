@@ -91,6 +91,57 @@ def test_few_tokens_split_k_down_gemm(T, E, topk, H, I):
     assert nc_part[:, 0].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("T,E,topk,H,I", [(1, 8, 2, 512, 256), (7, 64, 8, 1024, 256), (16, 16, 4, 256, 384), (17, 8, 2, 512, 256),
+                                          (32, 256, 8, 512, 128), (40, 8, 2, 256, 1152), (64, 8, 2, 512, 256)])
+def test_few_token_path_vs_oracle_and_tile_path(T, E, topk, H, I):
+    """T <= 64 takes the swapped-operand kernels (token tiles of 16 / 32 / 64, no align or gather pass).
+    Against the oracle, and against the 128 x 256 tile path on the same inputs (knob ``moe_decode=0``):
+    both quantise the token rows identically, so they differ only by the intermediate's quantisation
+    arithmetic and the summation order."""
+    from sglang_b200._native import tuning
+
+    g = torch.Generator().manual_seed(900 + T + E)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 60 + T)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), topk, True)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti)
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+    with tuning(moe_decode=0):
+        tile = _run(x, w1, w2, w1_s, w2_s, tw, ti)
+    assert O.rel_frobenius(out.float().cpu(), tile.float().cpu()) < TOL
+    # called again: same bits (no state is carried between calls)
+    assert torch.equal(_run(x, w1, w2, w1_s, w2_s, tw, ti), out)
+    # ids of other ranks, and the un-combined form
+    local = ti.clone()
+    local[::2, 0] = -1
+    part = _run(x, w1, w2, w1_s, w2_s, tw, local)
+    assert O.rel_frobenius(part.float().cpu(), O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, local, [128, 128])) < TOL
+    nc = _run(x, w1, w2, w1_s, w2_s, tw, ti, no_combine=True)
+    assert O.rel_frobenius(nc.float().cpu(), O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128], no_combine=True)) < TOL
+
+
+def test_few_token_path_router_weight_on_input_and_prequantised_rows():
+    import sglang_b200 as S
+    from sglang_b200.fused_moe import fused_experts_impl
+
+    T, E, H, I = 9, 8, 512, 256
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 78)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), 1, False)
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128], apply_router_weight_on_input=True)
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti, apply_router_weight_on_input=True)
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+    # rows that arrive quantised (what an expert-parallel dispatch delivers)
+    tw2, ti2 = O.softmax_topk(torch.randn(T, E, generator=g), 2, True)
+    q, s = S.per_token_group_quant_fp8(x.cuda(), 128)
+    got = fused_experts_impl(q, w1.cuda(), w2.cuda(), tw2.cuda(), ti2.cuda().int(), w1_s.cuda(), w2_s.cuda(), inplace=False,
+                             hidden_states_scale=s, output_dtype=torch.bfloat16)
+    _status_ok()
+    assert O.rel_frobenius(got.float().cpu(), O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw2, ti2, [128, 128])) < TOL
+
+
 def test_expert_parallel_minus_one_ids_sum_to_full_result():
     T, E, topk, H, I = 96, 16, 4, 512, 256
     g = torch.Generator().manual_seed(11)
