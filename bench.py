@@ -364,6 +364,13 @@ class TPLayers:
         S, outs = self.S, {}
         for name, n, k, kind, x, wq, ws in self.layers:
             xin = (inputs[name] if inputs is not None else x)[:rows]
+            if rows <= 16 and events is None and (kind == "column" or self.world == 1 or mode == "nccl"):
+                # decode size: the public linear (one launch: quantiser, GEMM and split-K sum)
+                out = S.w8a8_block_fp8_linear(xin, wq, [128, 128], ws)
+                if kind == "row" and self.world > 1:
+                    self.P.tensor_model_parallel_all_reduce(out)
+                outs[name] = out
+                continue
             q, s = S.per_token_group_quant_fp8(xin, 128, column_major_scales=True)
             if events is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

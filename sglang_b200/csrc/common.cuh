@@ -102,6 +102,17 @@ __device__ __forceinline__ uint4 ld_nc_16(const void* p) {
   return v;
 }
 
+// Four consecutive floats from shared memory, read at this point of the program (never cached in
+// registers across a barrier wait): for tables another warp fills while this one waits on an mbarrier.
+__device__ __forceinline__ float4 ld_shared_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p)))
+               : "memory");
+  return v;
+}
+
 // Four floats -> four E4M3 bytes (round-to-nearest-even, saturate to +-448), packed little-endian.
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
   __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);

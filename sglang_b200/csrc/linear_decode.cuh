@@ -35,7 +35,7 @@ struct DecodeLinearCfg {
   static constexpr int kStages = 5;
   static constexpr int kStageW = 128 * kBK;  // 16 KB of weights
   static constexpr int kStageX = NT * kBK;   // 2 KB of quantised activations
-  static constexpr int kThreads = 6 * 32;    // 4 quantise + promote warps, TMA producer, MMA issuer
+  static constexpr int kThreads = 10 * 32;   // 4 promotion warps, TMA producer, MMA issuer, 4 quantiser warps
   static constexpr int kTmemCols = 32;
   static constexpr int kMaxKb = 64;          // K blocks one CTA may own (scales staged in smem)
   static constexpr size_t kSmemBytes = (size_t)kStages * (kStageW + kStageX) + (size_t)kMaxKb * NT * 4 + 1024 + 256;
@@ -64,7 +64,7 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
   volatile int* last_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 6);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int kProducerWarp = 4, kMmaWarp = 5;
+  constexpr int kProducerWarp = 4, kMmaWarp = 5, kFirstQuantWarp = 6;
 
   const int item = blockIdx.x;
   const int ks = item % p.k_splits;
@@ -137,13 +137,15 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
       }
       __syncwarp();
     }
-  } else {
-    // ------------------------------------------- quantise x, then promote (lane = weight row)
+  } else if (warp >= kFirstQuantWarp) {
+    // --------------------------------------------------- quantiser warps: x -> FP8 stages
+    // They run ahead of the tensor core by up to S stages and fetch the rows of two K blocks at a time, so the
+    // L2 round trip of x is never on the path of the weight stream.
     // x (and the output / partial buffers) may belong to the kernel before this one in the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int tid = threadIdx.x;            // 0..127
-    const int q_row = tid >> 3;             // token row this thread quantises (8 threads per row)
-    const int q_chunk = tid & 7;            // 16-element chunk of the 128-wide group
+    const int tid = threadIdx.x - kFirstQuantWarp * 32;  // 0..127
+    const int q_row = tid >> 3;                            // token row this thread quantises (8 threads per row)
+    const int q_chunk = tid & 7;                           // 16-element chunk of the 128-wide group
     const bool q_live = q_row < p.M;
     const InT* x_row = static_cast<const InT*>(p.x) + (int64_t)(q_live ? q_row : 0) * p.K + q_chunk * 16;
     const float* bs_row = p.Bs + (int64_t)nt * p.num_kb;
@@ -151,16 +153,18 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
     // XORed with the row index inside the group (the 128-byte swizzle of the UMMA descriptor)
     const uint32_t q_off = (uint32_t)(q_row >> 3) * 1024u + (uint32_t)(q_row & 7) * 128u +
                            (uint32_t)((q_chunk ^ (q_row & 7)) << 4);
-    auto quantise = [&](int j) {  // K block kb0 + j -> stage j % S, scales[j][*]
+    auto fetch = [&](int j, float (&f)[16], float& bs) {
       const int kb = kb0 + j;
-      float f[16];
-      const bool in = q_live && kb * 128 + q_chunk * 16 < p.K;
+      const bool in = q_live && j < nkb && kb * 128 + q_chunk * 16 < p.K;
       if (in) {
         Vec16<InT>::load(x_row + (int64_t)kb * 128, f);
       } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) f[i] = 0.f;
       }
+      bs = q_live && j < nkb && q_chunk == 0 ? __ldg(bs_row + kb) : 0.f;
+    };
+    auto emit = [&](int j, const float (&f)[16], float bs) {  // K block kb0 + j -> stage j % S, scales[j][*]
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
@@ -169,54 +173,67 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
       const float sc = quant16(f, amax, B200_QUANT_DIV_CORRECTED, qv);
       if (!q_live) qv = make_uint4(0, 0, 0, 0);
       *reinterpret_cast<uint4*>(sX_ptr + (size_t)(j % S) * Cfg::kStageX + q_off) = qv;
-      if (q_chunk == 0) scales[j * NT + q_row] = q_live ? sc * __ldg(bs_row + kb) : 0.f;
-      // generic-proxy writes -> visible to the tensor core's (async proxy) reads of this stage
+      if (q_chunk == 0) scales[j * NT + q_row] = q_live ? sc * bs : 0.f;
+      // generic-proxy writes -> visible to the tensor core's (async proxy) reads of this stage, and the
+      // scale table to the promotion warps that read it after the MMA of this stage has completed
+      __threadfence_block();
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(full_bar(j % S));
     };
-    const int npro = min(S, nkb);
-    for (int j = 0; j < npro; ++j) quantise(j);
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the scales of the first K blocks are in place for all four warps
-
+    bool ok = true;
+    for (int j = 0; j < nkb && ok; j += 2) {
+      float f0[16], f1[16], b0, b1;
+      fetch(j, f0, b0);
+      fetch(j + 1, f1, b1);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int jj = j + u;
+        if (jj >= nkb) break;
+        if (jj >= S) {  // the stage is free once the MMAs that read it have completed
+          ok = ptx::mbar_wait(empty_bar(jj % S), ((jj / S) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+        }
+        if (u == 0) emit(jj, f0, b0);
+        else emit(jj, f1, b1);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ promotion warps (lane = weight row)
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // they write the output / partials at the end
+    const int tid = threadIdx.x;  // 0..127
     const int n = n0 + warp * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
     float acc[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t] = 0.f;
-    // A wait that gives up must not leave the other warps alone at the named barrier below: every warp
-    // reaches the barrier in every iteration and all of them leave the loop together on the abort flag.
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
       const int b = j & 1;
-      if (ok) ok = ptx::mbar_wait(tfull_bar(b), (j >> 1) & 1, abort_flag);
-      if (ok) {
-        ptx::tc_fence_after();
-        uint32_t v[32];
-        ptx::tmem_ld16(lane_base + b * NT, v);
-        ptx::tmem_ld_wait16(v);
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-        const float4* sc = reinterpret_cast<const float4*>(scales + (size_t)j * NT);
+      ok = ptx::mbar_wait(tfull_bar(b), (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      uint32_t v[32];
+      ptx::tmem_ld16(lane_base + b * NT, v);
+      ptx::tmem_ld_wait16(v);
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
+      // written by the quantiser warps before they released this stage to the tensor core
+      const float* sc = scales + (size_t)j * NT;
 #pragma unroll
-        for (int q = 0; q < NT / 4; ++q) {
-          const float4 s4 = sc[q];  // same address for every lane: broadcast
-          acc[4 * q + 0] = fmaf(__uint_as_float(v[4 * q + 0]), s4.x, acc[4 * q + 0]);
-          acc[4 * q + 1] = fmaf(__uint_as_float(v[4 * q + 1]), s4.y, acc[4 * q + 1]);
-          acc[4 * q + 2] = fmaf(__uint_as_float(v[4 * q + 2]), s4.z, acc[4 * q + 2]);
-          acc[4 * q + 3] = fmaf(__uint_as_float(v[4 * q + 3]), s4.w, acc[4 * q + 3]);
-        }
-        // the MMAs of K block j have completed (tfull), so stage j % S is free: refill it for K block j + S
-        if (j + S < nkb) quantise(j + S);
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abort_flag) {
-        ok = false;
-        break;
+      for (int q = 0; q < NT / 4; ++q) {
+        const float4 s4 = ld_shared_f4(sc + 4 * q);  // same address for every lane: broadcast
+        acc[4 * q + 0] = fmaf(__uint_as_float(v[4 * q + 0]), s4.x, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(__uint_as_float(v[4 * q + 1]), s4.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(__uint_as_float(v[4 * q + 2]), s4.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(__uint_as_float(v[4 * q + 3]), s4.w, acc[4 * q + 3]);
       }
     }
-    if (ok) {
+    // A wait that gave up must not leave the other warps alone at the named barriers below: all four warps
+    // meet here and take the same branch on the CTA-wide abort flag.
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!*abort_flag) {
       if (p.k_splits == 1) {
         if (n < p.N) {
           OutT* out = static_cast<OutT*>(p.out) + n;

@@ -53,7 +53,8 @@ struct MoeDecodeCfg {
   static constexpr int kCtasPerSm = NT == 64 ? 1 : 2;
   static constexpr int kStageW = 128 * kBK;
   static constexpr int kStageX = NT * kBK;
-  static constexpr int kThreads = 6 * 32;
+  static constexpr int kQuantWarps = NT == 64 ? 8 : 4;  // each thread quantises one or two (row, 16-element chunk) pairs per K block
+  static constexpr int kThreads = (6 + kQuantWarps) * 32;  // 4 promotion warps, TMA producer, MMA issuer, quantiser warps
   static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
   static constexpr int kMaxKb = 64;
   static constexpr int kScaleBytes = kMaxKb * NT * 4;
@@ -100,7 +101,7 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 5);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int kProducerWarp = 4, kMmaWarp = 5;
+  constexpr int kProducerWarp = 4, kMmaWarp = 5, kFirstQuantWarp = 6;
 
   // ---------------------------------------------------------------- which expert, which pairs
   // The routing (and, for the down stage, the activation rows) come from the kernels before this one.
@@ -233,60 +234,91 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
       }
       __syncwarp();
     }
-  } else {
-    // ------------------------------- token rows -> FP8 in shared memory, then promote (lane = weight row)
-    const int tid = threadIdx.x;  // 0..127
+  } else if (warp >= kFirstQuantWarp) {
+    // ------------------------------------ quantiser warps: token rows -> FP8 stages in shared memory
+    // They run ahead of the tensor core by up to S stages and fetch the rows of two K blocks at a time, so the
+    // L2 round trip of the rows is never on the path of the weight stream.
+    constexpr int kRowsPerThread = NT * 8 / (Cfg::kQuantWarps * 32);
+    constexpr int kRowStep = Cfg::kQuantWarps * 4;  // rows covered by one pass of the quantiser threads
+    const int tid = threadIdx.x - kFirstQuantWarp * 32;
     const int q_chunk = tid & 7;
+    struct Fetched {
+      float f[16];
+      uint4 raw;
+      float sc;
+    };
+    auto fetch = [&](int j, int rr, Fetched& d) {
+      const int kb = kb0 + j;
+      const int row = (tid >> 3) + kRowStep * rr;
+      const bool live = row < cnt && j < nkb;
+      d.raw = make_uint4(0, 0, 0, 0);
+      d.sc = 0.f;
+      if (STAGE == 1 && p.x_q != nullptr) {
+        // rows already quantised (expert-parallel receive area): bytes and scale as they are
+        if (live) {
+          const int64_t tok = pairs[row] / p.topk;
+          d.raw = ld_nc_16(p.x_q + tok * p.K + kb * 128 + q_chunk * 16);
+          if (q_chunk == 0) d.sc = __ldg(p.x_s + tok * p.num_kb + kb);
+        }
+      } else if (live) {
+        if (STAGE == 1) Vec16<InT>::load(static_cast<const InT*>(p.x) + (int64_t)(pairs[row] / p.topk) * p.K + kb * 128 + q_chunk * 16, d.f);
+        else load16_f32(p.act + (int64_t)pairs[row] * p.K + kb * 128 + q_chunk * 16, d.f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) d.f[i] = 0.f;
+      }
+    };
+    auto emit = [&](int j, int rr, const Fetched& d) {
+      const int row = (tid >> 3) + kRowStep * rr;
+      const bool live = row < cnt;
+      uint4 qv = d.raw;
+      float sc = d.sc;
+      if (!(STAGE == 1 && p.x_q != nullptr)) {
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(d.f[i]));
+        amax = fmaxf(group_max<8>(amax), 1e-10f);
+        // 16-bit rows: the division-free evaluation that equals x / (amax / 448) on every 16-bit input;
+        // fp32 rows (the activation between the two GEMMs): the division itself, as the oracle computes it
+        sc = quant16(d.f, amax, STAGE == 1 ? B200_QUANT_DIV_CORRECTED : B200_QUANT_DIV, qv);
+        if (!live) qv = make_uint4(0, 0, 0, 0);
+      }
+      const uint32_t off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u + (uint32_t)((q_chunk ^ (row & 7)) << 4);
+      *reinterpret_cast<uint4*>(sX_ptr + (size_t)(j % S) * Cfg::kStageX + off) = qv;
+      if (q_chunk == 0) scales[j * NT + row] = live ? sc : 0.f;
+    };
+    bool ok = true;
+    for (int j = 0; j < nkb && ok; j += 2) {
+      Fetched d[2][kRowsPerThread];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int rr = 0; rr < kRowsPerThread; ++rr) fetch(j + u, rr, d[u][rr]);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int jj = j + u;
+        if (jj >= nkb) break;
+        if (jj >= S) {  // the stage is free once the MMAs that read it have completed
+          ok = ptx::mbar_wait(empty_bar(jj % S), ((jj / S) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int rr = 0; rr < kRowsPerThread; ++rr) emit(jj, rr, d[u][rr]);
+        // generic-proxy writes -> visible to the tensor core's (async proxy) reads of this stage, and the
+        // scale table to the promotion warps that read it after the MMA of this stage has completed
+        __threadfence_block();
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(full_bar(jj % S));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ promotion warps (lane = weight row)
     // weight-scale rows: gate_up rows [tile*64..) live in block tile/2 of the gate half, the up rows in the
     // same block of the up half (n_out/128 blocks further); down: block `tile`
     const int blocks_per_expert = (STAGE == 1 ? 2 * p.n_out : p.n_out) / 128;
     const float* bs_a = p.Bs + ((int64_t)expert * blocks_per_expert + (STAGE == 1 ? tile / 2 : tile)) * p.num_kb;
     const float* bs_b = bs_a + (int64_t)(p.n_out / 128) * p.num_kb;  // STAGE 1: scales of the up rows
-    auto quantise = [&](int j) {  // K block kb0 + j -> stage j % S, scales[j][*]
-      const int kb = kb0 + j;
-#pragma unroll
-      for (int rr = 0; rr < NT / 16; ++rr) {
-        const int row = (tid >> 3) + 16 * rr;
-        const bool live = row < cnt;
-        uint4 qv = make_uint4(0, 0, 0, 0);
-        float sc = 0.f;
-        if (STAGE == 1 && p.x_q != nullptr) {
-          // rows already quantised (expert-parallel receive area): gather bytes and scale
-          if (live) {
-            const int64_t tok = pairs[row] / p.topk;
-            qv = ld_nc_16(p.x_q + tok * p.K + kb * 128 + q_chunk * 16);
-            if (q_chunk == 0) sc = __ldg(p.x_s + tok * p.num_kb + kb);
-          }
-        } else {
-          float f[16];
-          if (live) {
-            if (STAGE == 1) Vec16<InT>::load(static_cast<const InT*>(p.x) + (int64_t)(pairs[row] / p.topk) * p.K + kb * 128 + q_chunk * 16, f);
-            else load16_f32(p.act + (int64_t)pairs[row] * p.K + kb * 128 + q_chunk * 16, f);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) f[i] = 0.f;
-          }
-          float amax = 0.f;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-          amax = fmaxf(group_max<8>(amax), 1e-10f);
-          // 16-bit rows: the division-free evaluation that equals x / (amax / 448) on every 16-bit input;
-          // fp32 rows (the activation between the two GEMMs): the division itself, as the oracle computes it
-          sc = quant16(f, amax, STAGE == 1 ? B200_QUANT_DIV_CORRECTED : B200_QUANT_DIV, qv);
-          if (!live) qv = make_uint4(0, 0, 0, 0);
-        }
-        const uint32_t off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u + (uint32_t)((q_chunk ^ (row & 7)) << 4);
-        *reinterpret_cast<uint4*>(sX_ptr + (size_t)(j % S) * Cfg::kStageX + off) = qv;
-        if (q_chunk == 0) scales[j * NT + row] = live ? sc : 0.f;
-      }
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(full_bar(j % S));
-    };
-    const int npro = min(S, nkb);
-    for (int j = 0; j < npro; ++j) quantise(j);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-
     const int r = warp * 32 + lane;  // weight row of the tile
     // the block scale of this thread's weight row for every K block of the item
     const float* bs_mine = STAGE == 1 && r >= 64 ? bs_b : bs_a;
@@ -299,42 +331,39 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
     for (int j = 0; j < nkb; ++j) {
       const int b = j & 1;
       const float bsc_next = j + 1 < nkb ? __ldg(bs_mine + kb0 + j + 1) : 0.f;
-      if (ok) ok = ptx::mbar_wait(tfull_bar(b), (j >> 1) & 1, abort_flag);
-      if (ok) {
-        ptx::tc_fence_after();
-        uint32_t v[NT < 32 ? 32 : NT];
-        if constexpr (NT == 16) {
-          ptx::tmem_ld16(lane_base + b * NT, v);
-          ptx::tmem_ld_wait16(v);
-        } else if constexpr (NT == 32) {
-          ptx::tmem_ld32(lane_base + b * NT, v);
-          ptx::tmem_ld_wait(v);
-        } else {
-          ptx::tmem_ld64(lane_base + b * NT, v);
-          ptx::tmem_ld_wait64(v);
-        }
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-        const float4* sc = reinterpret_cast<const float4*>(scales + (size_t)j * NT);
+      ok = ptx::mbar_wait(tfull_bar(b), (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      uint32_t v[NT < 32 ? 32 : NT];
+      if constexpr (NT == 16) {
+        ptx::tmem_ld16(lane_base + b * NT, v);
+        ptx::tmem_ld_wait16(v);
+      } else if constexpr (NT == 32) {
+        ptx::tmem_ld32(lane_base + b * NT, v);
+        ptx::tmem_ld_wait(v);
+      } else {
+        ptx::tmem_ld64(lane_base + b * NT, v);
+        ptx::tmem_ld_wait64(v);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
+      // written by the quantiser warps before they released this stage to the tensor core
+      const float* sc = scales + (size_t)j * NT;
 #pragma unroll
-        for (int q = 0; q < NT / 4; ++q) {
-          const float4 s4 = sc[q];  // same address for every lane: broadcast
-          acc[4 * q + 0] = fmaf(__uint_as_float(v[4 * q + 0]), s4.x * bsc, acc[4 * q + 0]);
-          acc[4 * q + 1] = fmaf(__uint_as_float(v[4 * q + 1]), s4.y * bsc, acc[4 * q + 1]);
-          acc[4 * q + 2] = fmaf(__uint_as_float(v[4 * q + 2]), s4.z * bsc, acc[4 * q + 2]);
-          acc[4 * q + 3] = fmaf(__uint_as_float(v[4 * q + 3]), s4.w * bsc, acc[4 * q + 3]);
-        }
-        if (j + S < nkb) quantise(j + S);
+      for (int q = 0; q < NT / 4; ++q) {
+        const float4 s4 = ld_shared_f4(sc + 4 * q);  // same address for every lane: broadcast
+        acc[4 * q + 0] = fmaf(__uint_as_float(v[4 * q + 0]), s4.x * bsc, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(__uint_as_float(v[4 * q + 1]), s4.y * bsc, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(__uint_as_float(v[4 * q + 2]), s4.z * bsc, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(__uint_as_float(v[4 * q + 3]), s4.w * bsc, acc[4 * q + 3]);
       }
       bsc = bsc_next;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abort_flag) {
-        ok = false;
-        break;
-      }
     }
-    if (ok) {
+    // A wait that gave up must not leave the other warps alone at the named barrier below: all four warps
+    // meet here and take the same branch on the CTA-wide abort flag.
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!*abort_flag) {
       if (STAGE == 1) {
         if (p.weight_on_input) {
 #pragma unroll
