@@ -260,18 +260,6 @@ block_fp8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
           if (warp == 0 && lane == 0) ptx::mbar_arrive(empty_bar(it % S));  // MMAs done reading this stage
           ptx::tc_fence_after();
           const uint32_t ta = lane_base + b * BN;
-#if B200_PROMO >= 2
-          uint32_t v[64];
-          ptx::tmem_ld64(ta, v);
-          ptx::tmem_ld_wait64(v);
-          promote<64>(acc, v, sc);
-          ptx::tmem_ld64(ta + 64, v);
-          ptx::tmem_ld_wait64(v);
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(b ? leader_tempty1 : leader_tempty0);
-          promote<64>(acc + 64, v, sc);
-#else
           uint32_t va[32], vb[32];
           ptx::tmem_ld32(ta, va);
           ptx::tmem_ld_wait(va);
@@ -288,7 +276,6 @@ block_fp8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(b ? leader_tempty1 : leader_tempty0);
           promote32(acc + 96, vb, sc);
-#endif
           ++it;
         }
       }

@@ -185,32 +185,13 @@ __device__ __forceinline__ void store8<float>(float* dst, const float* a) {
   *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
 }
 
-#ifndef B200_PROMO
-#define B200_PROMO 0  // 0: scalar FMAs, x32 TMEM loads; 1: packed FMAs; 2: packed FMAs + x64 TMEM loads
-#endif
-#ifndef B200_MMA_N128
-#define B200_MMA_N128 0  // 1: the 256-wide tile is issued as two 128-wide MMAs per K step
-#endif
-
-// acc[0..CNT) += v[0..CNT) * scale
-template <int CNT>
-__device__ __forceinline__ void promote(float* acc, const uint32_t* v, float sc) {
-#if B200_PROMO >= 1 && B200_PROMO != 4
-  // packed fp32: one instruction per two accumulators
-  const float2 s2 = make_float2(sc, sc);
+// acc[0..32) += v[0..32) * scale. Packed fp32 FMAs (__ffma2_rn on register pairs) were measured 25 % slower
+// here, with and without float2 accumulators: the pairing constraints on 128 accumulators plus 64 staged
+// values cost more in spills and moves than the halved issue count saves.
+__device__ __forceinline__ void promote32(float* acc, const uint32_t (&v)[32], float sc) {
 #pragma unroll
-  for (int j = 0; j < CNT / 2; ++j) {
-    float2 a = make_float2(acc[2 * j], acc[2 * j + 1]);
-    a = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s2, a);
-    acc[2 * j] = a.x;
-    acc[2 * j + 1] = a.y;
-  }
-#else
-#pragma unroll
-  for (int j = 0; j < CNT; ++j) acc[j] = fmaf(__uint_as_float(v[j]), sc, acc[j]);
-#endif
+  for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v[j]), sc, acc[j]);
 }
-__device__ __forceinline__ void promote32(float* acc, const uint32_t (&v)[32], float sc) { promote<32>(acc, v, sc); }
 
 // tile index -> (m_tile, n_tile): sweep group_m row-tiles for every column tile before moving
 // on, so the CTAs running together share A rows and B columns in L2.
@@ -352,16 +333,6 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint64_t da = ptx::smem_desc_sw128(sA + s * Cfg::kStageA);
           const uint64_t db = ptx::smem_desc_sw128(sB + s * Cfg::kStageB);
           const uint32_t d = tmem_base + b * BN;
-#if B200_MMA_N128
-          if constexpr (BN == 256 && MODE != GEMM_GROUPED_SILU_QUANT) {
-            constexpr uint32_t idesc_h = ptx::idesc_e4m3_f32(kBM, 128);
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-              for (int k = 0; k < kBK / 32; ++k)  // B rows 128.. start 16 KB further: +1024 in the address field
-                ptx::mma_f8(d + h * 128, da + 2 * k, db + h * 1024 + 2 * k, idesc_h, k > 0);
-          } else
-#endif
 #pragma unroll
           for (int k = 0; k < kBK / 32; ++k)  // +32 bytes along K inside the swizzle row = +2 in the address field
             ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, k > 0);  // k == 0 overwrites the buffer
@@ -470,37 +441,6 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (warp == 0 && lane == 0) ptx::mbar_arrive(empty_bar(it % S));
           ptx::tc_fence_after();
           const uint32_t ta = lane_base + b * BN;
-#if B200_PROMO >= 3
-          // two TMEM loads in flight per wait: the buffer goes back to the MMA warp after two round trips
-          uint32_t va[32], vb[32];
-          ptx::tmem_ld32(ta, va);
-          ptx::tmem_ld32(ta + 32, vb);
-          ptx::tmem_ld_wait(va);
-          ptx::tmem_ld_wait(vb);
-          promote32(acc, va, sc);
-          ptx::tmem_ld32(ta + 64, va);
-          promote32(acc + 32, vb, sc);
-          ptx::tmem_ld32(ta + 96, vb);
-          ptx::tmem_ld_wait(va);
-          ptx::tmem_ld_wait(vb);
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-          promote32(acc + 64, va, sc2);
-          promote32(acc + 96, vb, sc2);
-#elif B200_PROMO >= 2
-          // two TMEM loads of 64 columns: the buffer goes back to the MMA warp after two round trips
-          uint32_t v[64];
-          ptx::tmem_ld64(ta, v);
-          ptx::tmem_ld_wait64(v);
-          promote<64>(acc, v, sc);
-          ptx::tmem_ld64(ta + 64, v);
-          ptx::tmem_ld_wait64(v);
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
-          promote<64>(acc + 64, v, sc2);
-#else
           uint32_t va[32], vb[32];
           // one TMEM load in flight behind the FMAs of the previous 32 columns
           ptx::tmem_ld32(ta, va);
@@ -519,7 +459,6 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
           promote32(acc + 96, vb, sc2);
-#endif
           ++it;
         }
       }

@@ -167,7 +167,7 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      ptx::mbar_init(full_bar(s), 1 + 4);
+      ptx::mbar_init(full_bar(s), 1 + Cfg::kQuantWarps);  // the producer's expect_tx + one arrival per quantiser warp
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
