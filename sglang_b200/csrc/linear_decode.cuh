@@ -153,18 +153,20 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
     // XORed with the row index inside the group (the 128-byte swizzle of the UMMA descriptor)
     const uint32_t q_off = (uint32_t)(q_row >> 3) * 1024u + (uint32_t)(q_row & 7) * 128u +
                            (uint32_t)((q_chunk ^ (q_row & 7)) << 4);
-    auto fetch = [&](int j, float (&f)[16], float& bs) {
+    // raw 16-bit elements of one (row, chunk): two 16-byte registers
+    auto fetch = [&](int j, uint4 (&raw)[2], float& bs) {
       const int kb = kb0 + j;
       const bool in = q_live && j < nkb && kb * 128 + q_chunk * 16 < p.K;
-      if (in) {
-        Vec16<InT>::load(x_row + (int64_t)kb * 128, f);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = 0.f;
-      }
+      const InT* src = x_row + (int64_t)kb * 128;
+      raw[0] = in ? ld_nc_16(src) : make_uint4(0, 0, 0, 0);
+      raw[1] = in ? ld_nc_16(src + 8) : make_uint4(0, 0, 0, 0);
       bs = q_live && j < nkb && q_chunk == 0 ? __ldg(bs_row + kb) : 0.f;
     };
-    auto emit = [&](int j, const float (&f)[16], float bs) {  // K block kb0 + j -> stage j % S, scales[j][*]
+    auto emit = [&](int j, const uint4 (&raw)[2], float bs) {  // K block kb0 + j -> stage j % S, scales[j][*]
+      float f[16];
+      const InT* e = reinterpret_cast<const InT*>(raw);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = to_f32<InT>(e[i]);
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
@@ -181,21 +183,24 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(full_bar(j % S));
     };
+    // Rows of kDepth K blocks are requested before any is used: under a saturated weight stream an L2 round
+    // trip takes microseconds, and the quantiser must deliver a K block every ~0.5 us to keep the stream going.
+    constexpr int kDepth = 4;
     bool ok = true;
-    for (int j = 0; j < nkb && ok; j += 2) {
-      float f0[16], f1[16], b0, b1;
-      fetch(j, f0, b0);
-      fetch(j + 1, f1, b1);
+    for (int j = 0; j < nkb && ok; j += kDepth) {
+      uint4 raw[kDepth][2];
+      float bs[kDepth];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < kDepth; ++u) fetch(j + u, raw[u], bs[u]);
+#pragma unroll
+      for (int u = 0; u < kDepth; ++u) {
         const int jj = j + u;
         if (jj >= nkb) break;
         if (jj >= S) {  // the stage is free once the MMAs that read it have completed
           ok = ptx::mbar_wait(empty_bar(jj % S), ((jj / S) & 1) ^ 1, abort_flag);
           if (!ok) break;
         }
-        if (u == 0) emit(jj, f0, b0);
-        else emit(jj, f1, b1);
+        emit(jj, raw[u], bs[u]);
       }
     }
   } else {

@@ -242,60 +242,81 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
     constexpr int kRowStep = Cfg::kQuantWarps * 4;  // rows covered by one pass of the quantiser threads
     const int tid = threadIdx.x - kFirstQuantWarp * 32;
     const int q_chunk = tid & 7;
+    // raw bytes of one (row, 16-element chunk): 16 B of FP8, 32 B of 16-bit or 64 B of fp32 values
+    constexpr bool kFp32Rows = STAGE == 2;
+    constexpr int kRawRegs = kFp32Rows ? 4 : 2;
     struct Fetched {
-      float f[16];
-      uint4 raw;
+      uint4 raw[kRawRegs];
       float sc;
     };
+    const bool prequantised = STAGE == 1 && p.x_q != nullptr;
     auto fetch = [&](int j, int rr, Fetched& d) {
       const int kb = kb0 + j;
       const int row = (tid >> 3) + kRowStep * rr;
       const bool live = row < cnt && j < nkb;
-      d.raw = make_uint4(0, 0, 0, 0);
-      d.sc = 0.f;
-      if (STAGE == 1 && p.x_q != nullptr) {
-        // rows already quantised (expert-parallel receive area): bytes and scale as they are
-        if (live) {
-          const int64_t tok = pairs[row] / p.topk;
-          d.raw = ld_nc_16(p.x_q + tok * p.K + kb * 128 + q_chunk * 16);
-          if (q_chunk == 0) d.sc = __ldg(p.x_s + tok * p.num_kb + kb);
-        }
-      } else if (live) {
-        if (STAGE == 1) Vec16<InT>::load(static_cast<const InT*>(p.x) + (int64_t)(pairs[row] / p.topk) * p.K + kb * 128 + q_chunk * 16, d.f);
-        else load16_f32(p.act + (int64_t)pairs[row] * p.K + kb * 128 + q_chunk * 16, d.f);
-      } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) d.f[i] = 0.f;
+      for (int i = 0; i < kRawRegs; ++i) d.raw[i] = make_uint4(0, 0, 0, 0);
+      d.sc = 0.f;
+      if (!live) return;
+      if (prequantised) {
+        // rows already quantised (expert-parallel receive area): bytes and scale as they are
+        const int64_t tok = pairs[row] / p.topk;
+        d.raw[0] = ld_nc_16(p.x_q + tok * p.K + kb * 128 + q_chunk * 16);
+        if (q_chunk == 0) d.sc = __ldg(p.x_s + tok * p.num_kb + kb);
+      } else if (STAGE == 1) {
+        const InT* src = static_cast<const InT*>(p.x) + (int64_t)(pairs[row] / p.topk) * p.K + kb * 128 + q_chunk * 16;
+        d.raw[0] = ld_nc_16(src);
+        d.raw[1] = ld_nc_16(src + 8);
+      } else {
+        // written by the kernel before this one: L2 loads
+        const uint4* src = reinterpret_cast<const uint4*>(p.act + (int64_t)pairs[row] * p.K + kb * 128 + q_chunk * 16);
+#pragma unroll
+        for (int i = 0; i < kRawRegs; ++i) d.raw[i] = __ldcg(src + i);
       }
     };
     auto emit = [&](int j, int rr, const Fetched& d) {
       const int row = (tid >> 3) + kRowStep * rr;
       const bool live = row < cnt;
-      uint4 qv = d.raw;
+      uint4 qv = d.raw[0];
       float sc = d.sc;
-      if (!(STAGE == 1 && p.x_q != nullptr)) {
+      if (!prequantised) {
+        float f[16];
+        if (kFp32Rows) {
+          const float* e = reinterpret_cast<const float*>(d.raw);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = e[i];
+        } else {
+          const InT* e = reinterpret_cast<const InT*>(d.raw);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = to_f32<InT>(e[i]);
+        }
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(d.f[i]));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
         amax = fmaxf(group_max<8>(amax), 1e-10f);
         // 16-bit rows: the division-free evaluation that equals x / (amax / 448) on every 16-bit input;
         // fp32 rows (the activation between the two GEMMs): the division itself, as the oracle computes it
-        sc = quant16(d.f, amax, STAGE == 1 ? B200_QUANT_DIV_CORRECTED : B200_QUANT_DIV, qv);
+        sc = quant16(f, amax, STAGE == 1 ? B200_QUANT_DIV_CORRECTED : B200_QUANT_DIV, qv);
         if (!live) qv = make_uint4(0, 0, 0, 0);
       }
       const uint32_t off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u + (uint32_t)((q_chunk ^ (row & 7)) << 4);
       *reinterpret_cast<uint4*>(sX_ptr + (size_t)(j % S) * Cfg::kStageX + off) = qv;
       if (q_chunk == 0) scales[j * NT + row] = live ? sc : 0.f;
     };
+    // Rows of kDepth K blocks are requested before any is used: under a saturated weight stream an L2 round
+    // trip takes microseconds, and the quantisers must deliver a K block every ~0.5 us to keep the stream going.
+    constexpr int kRegsPerBlock = kRawRegs * 4 * kRowsPerThread;  // registers one K block's rows occupy
+    constexpr int kDepth = 64 / kRegsPerBlock > 4 ? 4 : 64 / kRegsPerBlock;
+    static_assert(kDepth >= 2, "quantiser prefetch depth");
     bool ok = true;
-    for (int j = 0; j < nkb && ok; j += 2) {
-      Fetched d[2][kRowsPerThread];
+    for (int j = 0; j < nkb && ok; j += kDepth) {
+      Fetched d[kDepth][kRowsPerThread];
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
+      for (int u = 0; u < kDepth; ++u)
 #pragma unroll
         for (int rr = 0; rr < kRowsPerThread; ++rr) fetch(j + u, rr, d[u][rr]);
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < kDepth; ++u) {
         const int jj = j + u;
         if (jj >= nkb) break;
         if (jj >= S) {  // the stage is free once the MMAs that read it have completed
