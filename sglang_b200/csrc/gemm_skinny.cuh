@@ -29,7 +29,10 @@ struct SkinnyCfg {
   static constexpr int kStageW = 128 * kBK;  // 16 KB of weights
   static constexpr int kStageX = NT * kBK;   // 2 or 4 KB of activations
   static constexpr int kThreads = 6 * 32;    // 4 promotion warps, producer, MMA issuer
-  static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
+  // TMEM accumulator buffers: the tensor core runs this many K blocks ahead of the promotion warps, so the
+  // commit -> tcgen05.ld -> arrive round trip (about a microsecond) is off the per-K-block path
+  static constexpr int kAccBufs = 4;
+  static constexpr int kTmemCols = kAccBufs * NT;
   static constexpr int kMaxKb = 64;          // K blocks one CTA may own (scales staged in smem)
   static constexpr size_t kSmemBytes =
       (size_t)kStages * (kStageW + kStageX) + (size_t)kMaxKb * NT * 4 + 1024 + 256;
@@ -51,10 +54,11 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
   const uint32_t bar0 = ptx::smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  constexpr int NB = Cfg::kAccBufs;
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 5);
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + NB + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 * NB);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 2 * NB + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kProducerWarp = 4, kMmaWarp = 5;
@@ -72,7 +76,7 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NB; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
       ptx::mbar_init(tempty_bar(b), 4);
     }
@@ -143,8 +147,8 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
     bool ok = true;
     uint32_t it = 0;
     for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-      const int s = it % S, b = it & 1;
-      ok = ptx::mbar_wait(tempty_bar(b), ((it >> 1) & 1) ^ 1, abort_flag) &&
+      const int s = it % S, b = it % NB;
+      ok = ptx::mbar_wait(tempty_bar(b), ((it / NB) & 1) ^ 1, abort_flag) &&
            ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
@@ -169,8 +173,8 @@ block_fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const _
     bool ok = true;
     uint32_t it = 0;
     for (int kb = kb0; kb < kb1; ++kb, ++it) {
-      const int b = it & 1;
-      ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
+      const int b = it % NB;
+      ok = ptx::mbar_wait(tfull_bar(b), (it / NB) & 1, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
       uint32_t v[32];

@@ -36,7 +36,10 @@ struct DecodeLinearCfg {
   static constexpr int kStageW = 128 * kBK;  // 16 KB of weights
   static constexpr int kStageX = NT * kBK;   // 2 KB of quantised activations
   static constexpr int kThreads = 10 * 32;   // 4 promotion warps, TMA producer, MMA issuer, 4 quantiser warps
-  static constexpr int kTmemCols = 32;
+  // TMEM accumulator buffers: the tensor core runs this many K blocks ahead of the promotion warps, so the
+  // commit -> tcgen05.ld -> arrive round trip (about a microsecond) is off the per-K-block path
+  static constexpr int kAccBufs = 4;
+  static constexpr int kTmemCols = kAccBufs * NT;
   static constexpr int kMaxKb = 64;          // K blocks one CTA may own (scales staged in smem)
   static constexpr size_t kSmemBytes = (size_t)kStages * (kStageW + kStageX) + (size_t)kMaxKb * NT * 4 + 1024 + 256;
 };
@@ -57,11 +60,12 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
   const uint32_t bar0 = ptx::smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  constexpr int NB = Cfg::kAccBufs;
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 5);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 6);
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + NB + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 * NB);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 2 * NB + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 2 * NB + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kProducerWarp = 4, kMmaWarp = 5, kFirstQuantWarp = 6;
@@ -78,7 +82,7 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
       ptx::mbar_init(full_bar(s), 1 + 4);  // the producer's expect_tx + one arrival per quantising warp
       ptx::mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NB; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
       ptx::mbar_init(tempty_bar(b), 4);
     }
@@ -121,8 +125,8 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
     bool ok = true;
     uint32_t it = 0;
     for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-      const int s = it % S, b = it & 1;
-      ok = ptx::mbar_wait(tempty_bar(b), ((it >> 1) & 1) ^ 1, abort_flag) &&
+      const int s = it % S, b = it % NB;
+      ok = ptx::mbar_wait(tempty_bar(b), ((it / NB) & 1) ^ 1, abort_flag) &&
            ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
@@ -214,8 +218,8 @@ block_fp8_linear_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const
     for (int t = 0; t < NT; ++t) acc[t] = 0.f;
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
-      const int b = j & 1;
-      ok = ptx::mbar_wait(tfull_bar(b), (j >> 1) & 1, abort_flag);
+      const int b = j % NB;
+      ok = ptx::mbar_wait(tfull_bar(b), (j / NB) & 1, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
       uint32_t v[32];

@@ -55,7 +55,10 @@ struct MoeDecodeCfg {
   static constexpr int kStageX = NT * kBK;
   static constexpr int kQuantWarps = NT == 64 ? 8 : 4;  // each thread quantises one or two (row, 16-element chunk) pairs per K block
   static constexpr int kThreads = (6 + kQuantWarps) * 32;  // 4 promotion warps, TMA producer, MMA issuer, quantiser warps
-  static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
+  // TMEM accumulator buffers: the tensor core runs this many K blocks ahead of the promotion warps, so the
+  // commit -> tcgen05.ld -> arrive round trip (about a microsecond) is off the per-K-block path
+  static constexpr int kAccBufs = 4;
+  static constexpr int kTmemCols = kAccBufs * NT < 32 ? 32 : kAccBufs * NT;
   static constexpr int kMaxKb = 64;
   static constexpr int kScaleBytes = kMaxKb * NT * 4;
   static constexpr int kExchangeBytes = 64 * NT * 4;  // up rows handed to the gate rows' threads
@@ -95,10 +98,11 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
   const uint32_t bar0 = ptx::smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  constexpr int NB = Cfg::kAccBufs;
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 5);
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + NB + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 * NB);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * S + 2 * NB + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kProducerWarp = 4, kMmaWarp = 5, kFirstQuantWarp = 6;
@@ -170,7 +174,7 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
       ptx::mbar_init(full_bar(s), 1 + Cfg::kQuantWarps);  // the producer's expect_tx + one arrival per quantiser warp
       ptx::mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NB; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
       ptx::mbar_init(tempty_bar(b), 4);
     }
@@ -218,8 +222,8 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
     bool ok = true;
     uint32_t it = 0;
     for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-      const int s = it % S, b = it & 1;
-      ok = ptx::mbar_wait(tempty_bar(b), ((it >> 1) & 1) ^ 1, abort_flag) &&
+      const int s = it % S, b = it % NB;
+      ok = ptx::mbar_wait(tempty_bar(b), ((it / NB) & 1) ^ 1, abort_flag) &&
            ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
@@ -350,9 +354,9 @@ moe_decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const MoeDeco
     bool ok = true;
     float bsc = __ldg(bs_mine + kb0);
     for (int j = 0; j < nkb; ++j) {
-      const int b = j & 1;
+      const int b = j % NB;
       const float bsc_next = j + 1 < nkb ? __ldg(bs_mine + kb0 + j + 1) : 0.f;
-      ok = ptx::mbar_wait(tfull_bar(b), (j >> 1) & 1, abort_flag);
+      ok = ptx::mbar_wait(tfull_bar(b), (j / NB) & 1, abort_flag);
       if (!ok) break;
       ptx::tc_fence_after();
       uint32_t v[NT < 32 ? 32 : NT];
