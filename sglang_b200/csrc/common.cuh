@@ -54,7 +54,7 @@ struct Tuning {
   long gemm_splitk = -1;        // > 0: forced K split
   long gemm_2cta = -1;          // 0: never, 1: CTA-pair kernel whenever legal
   long linear_decode_fused = -1; // 0: callers keep quantiser + GEMM as separate launches at decode sizes
-  long moe_decode = -1;         // 0: fused_experts never takes the few-token (swapped-operand) path
+  long moe_decode = -1;         // 1: fused_experts takes the few-token (swapped-operand) path for T <= 64
   long moe_down_splitk = -1;    // 0: the down GEMM never splits K
   long moe_zero_pads = -1;      // 0 / 1: whether the gather pass zeroes pad rows
   long peer_wait_ms = -1;       // limit of a device-side wait for another GPU

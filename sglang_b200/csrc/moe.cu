@@ -335,7 +335,10 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   float* as1 = reinterpret_cast<float*>(ws + L.off_as1);
   uint8_t* aq2 = ws + L.off_aq2;
   float* as2 = reinterpret_cast<float*>(ws + L.off_as2);
-  if (L.decode && tuning().moe_decode != 0)
+  // Opt-in (knob moe_decode = 1): measured slower than the tile path below at every token count tried (the
+  // in-kernel row fetches sit behind the saturated weight stream in L2 and pace the pipeline, and more work
+  // items than resident CTAs run in waves), so the tile path stays the default.
+  if (L.decode && tuning().moe_decode == 1)
     return run_fused_experts_decode<T>(hidden, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T_tokens,
                                        topk, E, H, I, combine_mode, weight_on_input, routed_scale, ws, L, st);
   int down_splits = L.down_splits;

@@ -94,12 +94,17 @@ def test_few_tokens_split_k_down_gemm(T, E, topk, H, I):
 @pytest.mark.parametrize("T,E,topk,H,I", [(1, 8, 2, 512, 256), (7, 64, 8, 1024, 256), (16, 16, 4, 256, 384), (17, 8, 2, 512, 256),
                                           (32, 256, 8, 512, 128), (40, 8, 2, 256, 1152), (64, 8, 2, 512, 256)])
 def test_few_token_path_vs_oracle_and_tile_path(T, E, topk, H, I):
-    """T <= 64 takes the swapped-operand kernels (token tiles of 16 / 32 / 64, no align or gather pass).
-    Against the oracle, and against the 128 x 256 tile path on the same inputs (knob ``moe_decode=0``):
-    both quantise the token rows identically, so they differ only by the intermediate's quantisation
-    arithmetic and the summation order."""
+    """The swapped-operand kernels for T <= 64 (token tiles of 16 / 32 / 64, no align or gather pass; opt-in
+    with the knob ``moe_decode=1``). Against the oracle, and against the default 128 x 256 tile path on the
+    same inputs: both quantise the token rows identically, so they differ only by the intermediate's
+    quantisation arithmetic and the summation order."""
     from sglang_b200._native import tuning
 
+    with tuning(moe_decode=1):
+        _few_token_case(T, E, topk, H, I, tuning)
+
+
+def _few_token_case(T, E, topk, H, I, tuning):
     g = torch.Generator().manual_seed(900 + T + E)
     x = torch.randn(T, H, generator=g).bfloat16()
     w1, w2, w1_s, w2_s = _weights(E, I, H, 60 + T)
@@ -108,7 +113,7 @@ def test_few_token_path_vs_oracle_and_tile_path(T, E, topk, H, I):
     out = _run(x, w1, w2, w1_s, w2_s, tw, ti)
     assert O.rel_frobenius(out.float().cpu(), ref) < TOL
     with tuning(moe_decode=0):
-        tile = _run(x, w1, w2, w1_s, w2_s, tw, ti)
+        tile = _run(x, w1, w2, w1_s, w2_s, tw, ti)  # the default path
     assert O.rel_frobenius(out.float().cpu(), tile.float().cpu()) < TOL
     # called again: same bits (no state is carried between calls)
     assert torch.equal(_run(x, w1, w2, w1_s, w2_s, tw, ti), out)
@@ -122,6 +127,13 @@ def test_few_token_path_vs_oracle_and_tile_path(T, E, topk, H, I):
 
 
 def test_few_token_path_router_weight_on_input_and_prequantised_rows():
+    from sglang_b200._native import tuning
+
+    with tuning(moe_decode=1):
+        _few_token_other_inputs()
+
+
+def _few_token_other_inputs():
     import sglang_b200 as S
     from sglang_b200.fused_moe import fused_experts_impl
 
