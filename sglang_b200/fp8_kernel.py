@@ -292,15 +292,20 @@ def w8a8_block_fp8_linear(
 
 
 _tickets = {}
-DECODE_FUSED_MAX_M = 16
+# Rows up to which the one-launch kernel is taken. Measured on B200 (us, one launch / quantiser + GEMM + split-K sum,
+# weights rotated so that they come from HBM): 6144x4096 8.8/11.4 at M=1, 12.7/12.1 at M=4, 26.8/12.9 at M=16;
+# 4096x4096 6.7/10.8, 9.0/11.0, 16.9/11.6: the in-kernel quantisers pace the weight stream once many rows are live.
+DECODE_FUSED_MAX_M = 4
 
 
-def _linear_decode_fused(x: torch.Tensor, weight: torch.Tensor, block_size, weight_scale: torch.Tensor):
-    """At most 16 rows of 16-bit activations: quantiser, GEMM and split-K sum as ONE launch (every CTA
+def _linear_decode_fused(x: torch.Tensor, weight: torch.Tensor, block_size, weight_scale: torch.Tensor,
+                         max_rows: int = DECODE_FUSED_MAX_M):
+    """A few rows (the kernel takes up to 16, this wrapper sends it up to ``DECODE_FUSED_MAX_M``) of 16-bit
+    activations: quantiser, GEMM and split-K sum as ONE launch (every CTA
     quantises the slice of ``x`` it needs; same bytes and scales as ``per_token_group_quant_fp8``). Returns
     None when the shapes or dtypes are outside that kernel, and the caller takes the two-step path."""
     M, K = x.shape
-    if not (0 < M <= DECODE_FUSED_MAX_M and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
+    if not (0 < M <= max_rows and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
             and list(block_size) == [128, 128] and weight.dtype == fp8_dtype and weight.dim() == 2
             and weight_scale.dtype == torch.float32 and weight_scale.is_contiguous() and x.is_contiguous()
             and weight.is_contiguous() and K % 16 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] == K):

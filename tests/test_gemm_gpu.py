@@ -205,12 +205,17 @@ def test_one_launch_decode_linear(M, N, K, dtype):
     import sglang_b200 as S
     from sglang_b200._native import tuning
 
+    from sglang_b200 import fp8_kernel
+
     x = make_activation(M, K, 2300 + M + K, dtype=dtype)
     wq, ws = make_weight(N, K, 2301 + N)
     ref = O.w8a8_block_fp8_linear(x, wq, ws, output_dtype=torch.float32)
     xd, wd, sd = x.cuda(), wq.cuda(), ws.cuda()
-    out = S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd)
-    out2 = S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd)
+    # the kernel itself takes up to 16 rows; the public wrapper routes fewer rows to it by default
+    out = fp8_kernel._linear_decode_fused(xd, wd, [128, 128], sd, max_rows=16)
+    out2 = fp8_kernel._linear_decode_fused(xd, wd, [128, 128], sd, max_rows=16)
+    if M <= fp8_kernel.DECODE_FUSED_MAX_M:
+        assert torch.equal(S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd), out)
     with tuning(linear_decode_fused=0):
         two_step = S.w8a8_block_fp8_linear(xd, wd, [128, 128], sd)
     _status_ok()
