@@ -960,9 +960,15 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    stdout_fd = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout to the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # keep stdout to the one JSON line: libraries (NCCL's version banner among them) write to file
+        # descriptor 1 directly, so it points at stderr until the line is printed
+        sys.stdout.flush()
+        stdout_fd = os.dup(1)
+        os.dup2(2, 1)
         torch.distributed.init_process_group("nccl", device_id=device)
     import sglang_b200 as S
 
@@ -977,6 +983,9 @@ def main():
     # ------------------------------------------------------------------ parity gate of the headline
     parity = tp.check(M_ROWS, mode)
     if not parity["ok"]:
+        if stdout_fd is not None:
+            sys.stdout.flush()
+            os.dup2(stdout_fd, 1)
         if rank == 0:
             print(json.dumps({"metric": "block-FP8 GEMM TFLOPS", "value": None, "unit": "TFLOP/s", "n_gpus": world,
                               "error": "the headline workload failed its parity check; nothing was timed", "parity": parity}))
@@ -1156,9 +1165,14 @@ def main():
                     torch.cuda.synchronize()
                     torch.cuda.empty_cache()
             line["cpu_baseline"] = time_cpu_baseline()
+    if stdout_fd is not None:
+        sys.stdout.flush()
+        os.dup2(stdout_fd, 1)
+        os.close(stdout_fd)
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        os.dup2(2, 1)  # whatever the teardown prints is not part of the result
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
 

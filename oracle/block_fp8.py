@@ -63,6 +63,7 @@ __all__ = [
     "biased_grouped_topk",
     "sigmoid_topk",
     "grouped_topk",
+    "fused_shared_experts_tail",
     "canonical_routing",
     "ep_local_expert_ids",
     "rel_frobenius",
@@ -442,6 +443,23 @@ def grouped_topk(logits: torch.Tensor, topk: int, num_expert_group: int, topk_gr
     if renormalize:
         w = w / w.sum(dim=-1, keepdim=True)
     return w.to(torch.float32), ids.to(torch.int32)
+
+
+def fused_shared_experts_tail(raw_w: torch.Tensor, ids: torch.Tensor, renormalize: bool,
+                              routed_scaling_factor: Optional[float], apply_routed_scaling_factor_on_output: bool):
+    """Weights of the grouped routing functions when shared experts are fused into the routed ones
+    (python/sglang/srt/layers/moe/topk.py:735-764 and :968-992): ``raw_w`` / ``ids`` are the un-normalised top-k
+    in descending order. The last slot goes to a shared-expert replica (its id is drawn at random by the
+    reference, so only the routed ids ``ids[:, :-1]`` are comparable) with weight ``sum(routed) /
+    routed_scaling_factor``; renormalisation divides by the sum of the routed slots."""
+    w = raw_w.clone().float()
+    if routed_scaling_factor is not None:
+        w[:, -1] = w[:, :-1].sum(dim=-1) / routed_scaling_factor
+    if renormalize:
+        w = w / w[:, :-1].sum(dim=-1, keepdim=True)
+        if apply_routed_scaling_factor_on_output:
+            w = w * routed_scaling_factor
+    return w.to(torch.float32), ids[:, :-1].to(torch.int32)
 
 
 def canonical_routing(w: torch.Tensor, ids: torch.Tensor):

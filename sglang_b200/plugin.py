@@ -36,15 +36,15 @@ def biased_grouped_topk_around(original_fn, hidden_states, gating_output, correc
                                num_expert_group=None, topk_group=None, num_fused_shared_experts=0,
                                routed_scaling_factor=None, apply_routed_scaling_factor_on_output=False):
     """AROUND hook for ``biased_grouped_topk_gpu`` (python/sglang/srt/layers/moe/topk.py:1022-1033):
-    the B200 routing kernel unless fused shared experts are asked for."""
+    the B200 routing kernel for CUDA tensors (fused shared experts included)."""
     from . import topk as routing
 
-    if num_fused_shared_experts or not gating_output.is_cuda:
+    if not gating_output.is_cuda:
         return original_fn(hidden_states, gating_output, correction_bias, topk, renormalize, num_expert_group,
                            topk_group, num_fused_shared_experts, routed_scaling_factor,
                            apply_routed_scaling_factor_on_output)
     return routing.biased_grouped_topk(hidden_states, gating_output, correction_bias, topk, renormalize,
-                                       num_expert_group, topk_group, 0, routed_scaling_factor,
+                                       num_expert_group, topk_group, num_fused_shared_experts, routed_scaling_factor,
                                        apply_routed_scaling_factor_on_output)
 
 

@@ -143,6 +143,33 @@ def moe_fused_gate(
     return _route(input_tensor, topk, True, SIGMOID, bias, num_expert_group, topk_group, GROUP_TOP2_SUM, scale)
 
 
+def _with_fused_shared_experts(raw_weights: torch.Tensor, topk_ids: torch.Tensor, num_experts: int,
+                               num_fused_shared_experts: int, renormalize: bool, routed_scaling_factor: Optional[float],
+                               apply_routed_scaling_factor_on_output: bool,
+                               num_token_non_padded: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The tail of the reference's grouped routing functions when shared experts are fused into the routed ones
+    (topk.py:735-764, 968-992): ``raw_weights`` / ``topk_ids`` are the un-normalised top-k in descending order;
+    the LAST slot is handed to a shared-expert replica drawn uniformly from ``[num_experts, num_experts +
+    num_fused_shared_experts)`` with weight ``sum(routed weights) / routed_scaling_factor`` (left as it is when
+    no factor is given), and renormalisation divides by the sum of the routed slots only. A handful of
+    elementwise torch ops on ``[T, k]`` tensors; the selection itself is the CUDA kernel's."""
+    T, k = topk_ids.shape
+    assert k >= 2, "fused shared experts need at least one routed slot"
+    weights, ids = raw_weights.clone(), topk_ids.clone()
+    ids[:, -1] = torch.randint(num_experts, num_experts + num_fused_shared_experts, (T,), dtype=ids.dtype, device=ids.device)
+    routed_sum = weights[:, :-1].sum(dim=-1)
+    if routed_scaling_factor is not None:
+        weights[:, -1] = routed_sum / routed_scaling_factor
+    if renormalize:
+        weights = weights / routed_sum.unsqueeze(-1)
+        if apply_routed_scaling_factor_on_output:
+            weights = weights * routed_scaling_factor
+    if num_token_non_padded is not None:  # rows past the real tokens carry id -1, as without shared experts
+        pad = torch.arange(T, device=ids.device) >= num_token_non_padded.to(ids.device)
+        ids[pad] = -1
+    return weights.to(torch.float32), ids.to(torch.int32)
+
+
 # --------------------------------------------------------------------- topk.py functions
 def fused_topk(
     hidden_states: torch.Tensor,
@@ -177,7 +204,10 @@ def grouped_topk(
     """Softmax scores, a group's score is its maximum (DeepSeek-V2 routing)."""
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
     if num_fused_shared_experts:
-        raise NotImplementedError("fused shared experts are not part of this path")
+        raw, ids = _route(gating_output, topk, False, SOFTMAX, None, num_expert_group, topk_group, GROUP_MAX, 1.0)
+        return _with_fused_shared_experts(raw, ids, gating_output.shape[1], num_fused_shared_experts, renormalize,
+                                          routed_scaling_factor, apply_routed_scaling_factor_on_output,
+                                          num_token_non_padded)
     scale = 1.0
     if renormalize and apply_routed_scaling_factor_on_output and routed_scaling_factor is not None:
         scale = routed_scaling_factor
@@ -203,7 +233,11 @@ def biased_grouped_topk(
     scores, renormalised (DeepSeek-V3 routing)."""
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
     if num_fused_shared_experts:
-        raise NotImplementedError("fused shared experts are not part of this path")
+        raw, ids = _route(gating_output, topk, False, SIGMOID, correction_bias, num_expert_group, topk_group,
+                          GROUP_TOP2_SUM, 1.0)
+        return _with_fused_shared_experts(raw, ids, gating_output.shape[1], num_fused_shared_experts, renormalize,
+                                          routed_scaling_factor, apply_routed_scaling_factor_on_output,
+                                          num_token_non_padded)
     scale = 1.0
     if renormalize and apply_routed_scaling_factor_on_output and routed_scaling_factor is not None:
         scale = routed_scaling_factor

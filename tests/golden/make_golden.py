@@ -242,6 +242,29 @@ def main():
     ow, oi = O.grouped_topk(logits, 6, 8, 3, True)
     same_routing(rw, ri, ow, oi)
     out["grouped_softmax/logits"], out["grouped_softmax/w"], out["grouped_softmax/ids"] = raw(logits), raw(rw), raw(ri)
+    # shared experts fused into the routed ones: the reference replaces the last (smallest) slot of the sorted
+    # top-k by a shared-expert replica drawn at random, so the weights and the routed ids are what is pinned
+    impl = RT.biased_grouped_topk_impl
+    impl = getattr(impl, "_torchdynamo_orig_callable", None) or getattr(impl, "__wrapped__", impl)
+    logits = torch.randn(13, 256)
+    bias = torch.randn(256) * 0.01
+    rw, ri = impl(torch.zeros(13, 4), logits, bias, 9, True, 8, 4, 2, 2.5, False)
+    raw_w, raw_i = O.biased_grouped_topk(logits, bias, 9, 8, 4, False)
+    ow, oi = O.fused_shared_experts_tail(raw_w, raw_i, True, 2.5, False)
+    assert torch.equal(ri[:, :-1], oi) and bool(((ri[:, -1] >= 256) & (ri[:, -1] < 258)).all())
+    torch.testing.assert_close(rw, ow, rtol=1e-6, atol=0)
+    out["grouped_shared/logits"], out["grouped_shared/bias"] = raw(logits), raw(bias)
+    out["grouped_shared/w"], out["grouped_shared/routed_ids"] = raw(rw), raw(ri[:, :-1].contiguous())
+    impl = RT.grouped_topk_gpu
+    impl = getattr(impl, "_torchdynamo_orig_callable", None) or getattr(impl, "__wrapped__", impl)
+    logits = torch.randn(11, 160)
+    rw, ri = impl(torch.zeros(11, 4), logits, 7, True, 8, 3, 1, 16.0, True)
+    raw_w, raw_i = O.grouped_topk(logits, 7, 8, 3, False)
+    ow, oi = O.fused_shared_experts_tail(raw_w, raw_i, True, 16.0, True)
+    assert torch.equal(ri[:, :-1], oi) and bool((ri[:, -1] == 160).all())
+    torch.testing.assert_close(rw, ow, rtol=1e-6, atol=0)
+    out["grouped_softmax_shared/logits"], out["grouped_softmax_shared/w"] = raw(logits), raw(rw)
+    out["grouped_softmax_shared/routed_ids"] = raw(ri[:, :-1].contiguous())
     np.savez_compressed(os.path.join(HERE, "routing.npz"), **out)
     print("routing ok")
 

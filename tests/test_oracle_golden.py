@@ -87,6 +87,22 @@ def test_routing_matches_reference_vectors():
     _same_routing(w, ids, torch.from_numpy(g["w"]), torch.from_numpy(g["ids"]))
 
 
+def test_fused_shared_experts_tail_matches_reference_vectors():
+    """Shared experts fused into the routed ones (topk.py:735-764, 968-992): the weights of all k slots and
+    the routed ids (the shared slot's id is drawn at random by the reference)."""
+    c = load_golden("routing.npz")
+    g = c["grouped_shared"]
+    raw_w, raw_i = O.biased_grouped_topk(torch.from_numpy(g["logits"]), torch.from_numpy(g["bias"]), 9, 8, 4, False)
+    w, routed = O.fused_shared_experts_tail(raw_w, raw_i, True, 2.5, False)
+    assert torch.equal(routed, torch.from_numpy(g["routed_ids"]))
+    torch.testing.assert_close(w, torch.from_numpy(g["w"]), rtol=1e-6, atol=0)
+    g = c["grouped_softmax_shared"]
+    raw_w, raw_i = O.grouped_topk(torch.from_numpy(g["logits"]), 7, 8, 3, False)
+    w, routed = O.fused_shared_experts_tail(raw_w, raw_i, True, 16.0, True)
+    assert torch.equal(routed, torch.from_numpy(g["routed_ids"]))
+    torch.testing.assert_close(w, torch.from_numpy(g["w"]), rtol=1e-6, atol=0)
+
+
 def test_align_docstring_example():
     c = load_golden("align.npz")["doc"]
     s, e, n, cum = O.moe_align_block_size(torch.from_numpy(c["topk_ids"]), int(c["block_size"]), int(c["num_experts"]))

@@ -45,6 +45,31 @@ def test_reference_vectors():
     _same(w, ids, torch.from_numpy(g["w"]), torch.from_numpy(g["ids"]))
 
 
+def test_fused_shared_experts_reference_vectors():
+    """``num_fused_shared_experts > 0``: routed slots and all weights against the reference's vectors; the shared
+    slot's id is random in the reference, so it is checked for its range."""
+    from sglang_b200 import topk as R
+
+    c = load_golden("routing.npz")
+    g = c["grouped_shared"]
+    x = torch.from_numpy(g["logits"]).cuda()
+    w, ids = R.biased_grouped_topk(x, x, torch.from_numpy(g["bias"]).cuda(), 9, True, 8, 4, 2, 2.5, False)
+    assert w.dtype == torch.float32 and ids.dtype == torch.int32 and tuple(ids.shape) == (13, 9)
+    assert torch.equal(ids[:, :-1].cpu(), torch.from_numpy(g["routed_ids"]))
+    assert bool(((ids[:, -1] >= 256) & (ids[:, -1] < 258)).all())
+    torch.testing.assert_close(w.cpu(), torch.from_numpy(g["w"]), rtol=RTOL, atol=ATOL)
+    g = c["grouped_softmax_shared"]
+    x = torch.from_numpy(g["logits"]).cuda()
+    w, ids = R.grouped_topk(x, x, 7, True, 8, 3, 1, 16.0, True)
+    assert torch.equal(ids[:, :-1].cpu(), torch.from_numpy(g["routed_ids"])) and bool((ids[:, -1] == 160).all())
+    torch.testing.assert_close(w.cpu(), torch.from_numpy(g["w"]), rtol=RTOL, atol=ATOL)
+    # through the config dispatch, with padded rows masked
+    cfg = R.TopKConfig(top_k=7, use_grouped_topk=True, topk_group=3, num_expert_group=8, renormalize=True,
+                       num_fused_shared_experts=1, routed_scaling_factor=16.0, apply_routed_scaling_factor_on_output=True)
+    out = R.select_experts(x, x, cfg, num_token_non_padded=torch.tensor(5, device="cuda"))
+    assert torch.equal(out.topk_ids[:5], ids[:5]) and bool((out.topk_ids[5:] == -1).all())
+
+
 @pytest.mark.parametrize("T,E,topk", [(1, 8, 2), (17, 8, 2), (64, 60, 4), (333, 128, 8), (16, 256, 8), (5, 1024, 32),
                                       (7, 48, 3), (4097, 64, 6), (3, 2, 1), (9, 33, 33 - 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
@@ -127,8 +152,8 @@ def test_order_ties_padding_and_config_dispatch():
     assert tuple(w.shape) == (0, 2)
     with pytest.raises(AssertionError):
         R.fused_topk(x, x, 300, True)
-    with pytest.raises(NotImplementedError):
-        R.biased_grouped_topk(x, x, torch.zeros(256, device="cuda"), 8, True, 8, 4, num_fused_shared_experts=1)
+    with pytest.raises(NotImplementedError):  # the sgl-kernel style fused gate does not take shared experts here
+        R.moe_fused_gate(x, torch.zeros(256, device="cuda"), 8, 4, 8, num_fused_shared_experts=1)
 
 
 def test_routing_feeds_fused_experts_under_graph_capture():
