@@ -574,7 +574,8 @@ def bench_comparators(S, device):
     for i, (label, m, n, k) in enumerate(shapes):
         g = torch.Generator(device=device).manual_seed(8100 + i)
         x = torch.randn(m, k, device=device, generator=g).bfloat16()
-        wq, ws = synthetic.block_quant_weight_fp8((torch.randn(n, k, device=device, generator=g) * 0.02).bfloat16())
+        w_bf16 = (torch.randn(n, k, device=device, generator=g) * 0.02).bfloat16()
+        wq, ws = synthetic.block_quant_weight_fp8(w_bf16)
         q, s = S.per_token_group_quant_fp8(x, 128, column_major_scales=True)  # s: [m, k/128], stride (1, m)
         ours = S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)
         fl = 2.0 * m * n * k
@@ -601,6 +602,25 @@ def bench_comparators(S, device):
             except Exception as e:
                 item[key] = {"unavailable": repr(e)[:300]}
                 torch.cuda.synchronize()
+        # the same layer with power-of-two (UE8M0) scales, the format the reference's DeepGEMM path uses on this
+        # GPU: the block-scaled tensor-core kernel (no promotion) against the promotion kernel on the same bytes
+        try:
+            from sglang_b200 import _native, weight_quant as W
+
+            wq2, ws2 = W.quant_weight_ue8m0(w_bf16)
+            ws2p = W.transform_scale_ue8m0(ws2, mn=n)
+            q2, s2 = S.per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+            o2 = S.w8a8_block_fp8_matmul(q2, wq2, s2, ws2p, [128, 128], torch.bfloat16)
+            with _native.tuning(gemm_ue8m0=0):
+                o2_ref = S.w8a8_block_fp8_matmul(q2, wq2, s2, ws2p, [128, 128], torch.bfloat16)
+            us = graph_time_us([lambda: S.w8a8_block_fp8_matmul(q2, wq2, s2, ws2p, [128, 128], torch.bfloat16)] * 4)
+            item["ours_ue8m0_block_scaled_mma"] = {"us": us, "tflops": fl / us / 1e6,
+                                                   "rel_frob_vs_promotion_kernel_same_bytes": rel(o2, o2_ref)}
+            del wq2, ws2, ws2p, q2, s2, o2, o2_ref
+        except Exception as e:
+            item["ours_ue8m0_block_scaled_mma"] = {"unavailable": repr(e)[:300]}
+            torch.cuda.synchronize()
+        del w_bf16
         key = "vllm_cutlass_sm100"
         if vllm_err is not None:
             item[key] = {"unavailable": vllm_err}

@@ -115,6 +115,22 @@ int b200_w8a8_block_fp8_gemm(const void* A, const float* As, int64_t as_stride_m
                              size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * w8a8_block_fp8_matmul with power-of-two (UE8M0) scales applied inside the tensor core
+ * replaces: the DeepGEMM path the reference takes on Blackwell for block-FP8 linears
+ *           (python/sglang/srt/layers/quantization/fp8_utils.py:466-540 deepgemm_w8a8_block_fp8_linear_with_fallback,
+ *            scales prepared by :1209-1334 requant_weight_ue8m0 / transform_scale_ue8m0 and the
+ *            scale_ue8m0 form of per_token_group_quant_fp8, fp8_kernel.py:498-610)
+ * C[m,n] = sum_k A[m,k] * B[n,k] * 2^(ea[m,k/128]-127) * 2^(eb[n,k/128]-127), fp32 accumulation over the whole
+ * K in tensor memory (tcgen05.mma.kind::mxf8f6f4.block_scale): no per-K-block promotion.
+ * A [M,K] e4m3 row-major, B [N,K] e4m3 row-major. sfa: int32 words, word [g*sfa_ld + m] holds the exponent
+ * bytes of row m for the 128-K blocks 4g..4g+3 (byte kb%4; the packed MN-major layout of the reference,
+ * sfa_ld = rows padded to a multiple of 4). sfb: the same for the rows of B (sfb_rows_per_word = 1) or for its
+ * 128-row blocks (sfb_rows_per_word = 128). C [M,N] bf16/f16/f32. K % 16 == 0, N % 8 == 0; no workspace. */
+int b200_w8a8_block_fp8_gemm_ue8m0(const void* A, const int32_t* sfa, int64_t sfa_ld, const void* B,
+                                   const int32_t* sfb, int64_t sfb_ld, int sfb_rows_per_word, void* C,
+                                   int c_dtype, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * w8a8_block_fp8_linear at decode size: quantise + GEMM + split-K sum in ONE launch
  * replaces: the composition of python/sglang/srt/layers/quantization/fp8_utils.py:814-834
  *           (per_token_group_quant_fp8, then w8a8_block_fp8_matmul) for M <= 16 rows; the
@@ -153,6 +169,22 @@ int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel
                               int64_t max_pad, int32_t* expert_ids, int64_t max_blocks,
                               int32_t* num_post_pad, int32_t* cumsum, int pad_sorted,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * w8a8_block_fp8_matmul with power-of-two (UE8M0) scales applied inside the tensor core
+ * replaces: the DeepGEMM path the reference takes on Blackwell for block-FP8 linears
+ *           (python/sglang/srt/layers/quantization/fp8_utils.py:466-540 deepgemm_w8a8_block_fp8_linear_with_fallback,
+ *            scales prepared by :1209-1334 requant_weight_ue8m0 / transform_scale_ue8m0 and the
+ *            scale_ue8m0 form of per_token_group_quant_fp8, fp8_kernel.py:498-610)
+ * C[m,n] = sum_k A[m,k] * B[n,k] * 2^(ea[m,k/128]-127) * 2^(eb[n,k/128]-127), fp32 accumulation over the whole
+ * K in tensor memory (tcgen05.mma.kind::mxf8f6f4.block_scale): no per-K-block promotion.
+ * A [M,K] e4m3 row-major, B [N,K] e4m3 row-major. sfa: int32 words, word [g*sfa_ld + m] holds the exponent
+ * bytes of row m for the 128-K blocks 4g..4g+3 (byte kb%4; the packed MN-major layout of the reference,
+ * sfa_ld = rows padded to a multiple of 4). sfb: the same for the rows of B (sfb_rows_per_word = 1) or for its
+ * 128-row blocks (sfb_rows_per_word = 128). C [M,N] bf16/f16/f32. K % 16 == 0, N % 8 == 0; no workspace. */
+int b200_w8a8_block_fp8_gemm_ue8m0(const void* A, const int32_t* sfa, int64_t sfa_ld, const void* B,
+                                   const int32_t* sfb, int64_t sfb_ld, int sfb_rows_per_word, void* C,
+                                   int c_dtype, int64_t M, int64_t N, int64_t K, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * w8a8_block_fp8_linear at decode size: quantise + GEMM + split-K sum in ONE launch

@@ -38,6 +38,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
          c_void_p, c_size_t, c_void_p],
     ),
+    "b200_w8a8_block_fp8_gemm_ue8m0": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int64, c_int64, c_int64,
+         c_void_p],
+    ),
     "b200_w8a8_block_fp8_linear_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "b200_w8a8_block_fp8_linear_decode": (
         c_int,

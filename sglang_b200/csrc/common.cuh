@@ -53,6 +53,7 @@ struct Tuning {
   long gemm_skinny_max_m = -1;  // rows up to which the decode kernel is used
   long gemm_splitk = -1;        // > 0: forced K split
   long gemm_2cta = -1;          // 0: never, 1: CTA-pair kernel whenever legal
+  long gemm_ue8m0 = -1;          // 0: packed power-of-two scales never take the block-scaled MMA kernel
   long linear_decode_fused = -1; // 0: callers keep quantiser + GEMM as separate launches at decode sizes
   long moe_decode = -1;         // 1: fused_experts takes the few-token (swapped-operand) path for T <= 64
   long moe_down_splitk = -1;    // 0: the down GEMM never splits K

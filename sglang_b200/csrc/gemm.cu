@@ -4,6 +4,7 @@
 #include "gemm_2cta.cuh"
 #include "gemm_skinny.cuh"
 #include "linear_decode.cuh"
+#include "gemm_ue8m0.cuh"
 
 namespace b200 {
 
@@ -250,4 +251,32 @@ extern "C" int b200_w8a8_block_fp8_linear_decode(const void* x, int x_dtype, con
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (x_dtype == B200_BF16) return launch_decode_linear<__nv_bfloat16, __nv_bfloat16>(B, p, st);
   return launch_decode_linear<__half, __half>(B, p, st);
+}
+
+extern "C" int b200_w8a8_block_fp8_gemm_ue8m0(const void* A, const int32_t* sfa, int64_t sfa_ld, const void* B,
+                                              const int32_t* sfb, int64_t sfb_ld, int sfb_rows_per_word, void* C,
+                                              int c_dtype, int64_t M, int64_t N, int64_t K, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(M >= 0 && N >= 0 && K > 0, "gemm_ue8m0: bad shape");
+  if (M == 0 || N == 0) return B200_OK;
+  B200_CHECK_ARG(A && B && C && sfa && sfb, "gemm_ue8m0: null pointer");
+  B200_CHECK_ARG(((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 && ((uintptr_t)C & 15) == 0,
+                 "gemm_ue8m0: A, B and C must be 16-byte aligned");
+  B200_CHECK_ARG(sfb_rows_per_word == 1 || sfb_rows_per_word == 128, "gemm_ue8m0: one scale word per row or per 128 rows of B");
+  B200_CHECK_ARG(sfa_ld >= M && sfb_ld >= cdiv(N, sfb_rows_per_word), "gemm_ue8m0: scale row pitch shorter than the rows");
+  B200_UNSUPPORTED(K % 16 != 0 || N % 8 != 0, "gemm_ue8m0: K=%lld must be a multiple of 16, N=%lld of 8", (long long)K,
+                   (long long)N);
+  B200_UNSUPPORTED(M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL, "gemm_ue8m0: dimension too large");
+  Ue8m0Params p = {};
+  p.sfa = sfa; p.sfb = sfb; p.sfa_ld = sfa_ld; p.sfb_ld = sfb_ld; p.sfb_rows_per_word = sfb_rows_per_word;
+  p.C = C; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (c_dtype) {
+    case B200_BF16: return launch_gemm_ue8m0<__nv_bfloat16>(A, B, p, st);
+    case B200_F16: return launch_gemm_ue8m0<__half>(A, B, p, st);
+    case B200_F32: return launch_gemm_ue8m0<float>(A, B, p, st);
+    default:
+      set_error_detail("gemm_ue8m0: unknown output dtype code %d", c_dtype);
+      return B200_E_BAD_ARG;
+  }
 }

@@ -63,7 +63,7 @@ static long* tuning_slot(const char* name) {
   b200::Tuning& t = b200::tuning();
   struct { const char* n; long* p; } table[] = {
       {"gemm_bn", &t.gemm_bn}, {"gemm_skinny", &t.gemm_skinny}, {"gemm_skinny_max_m", &t.gemm_skinny_max_m},
-      {"gemm_splitk", &t.gemm_splitk}, {"gemm_2cta", &t.gemm_2cta}, {"linear_decode_fused", &t.linear_decode_fused}, {"moe_decode", &t.moe_decode}, {"moe_down_splitk", &t.moe_down_splitk},
+      {"gemm_splitk", &t.gemm_splitk}, {"gemm_2cta", &t.gemm_2cta}, {"gemm_ue8m0", &t.gemm_ue8m0}, {"linear_decode_fused", &t.linear_decode_fused}, {"moe_decode", &t.moe_decode}, {"moe_down_splitk", &t.moe_down_splitk},
       {"moe_zero_pads", &t.moe_zero_pads}, {"peer_wait_ms", &t.peer_wait_ms}};
   for (auto& e : table)
     if (name && strcmp(name, e.n) == 0) return e.p;

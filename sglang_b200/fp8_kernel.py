@@ -219,6 +219,49 @@ def reserve_workspace(max_bytes: int, device=None) -> None:
     _workspace(device, int(max_bytes))
 
 
+UE8M0_MIN_M = 65  # fewer rows: the decode kernel (weights streamed once) on the unpacked scales
+
+
+def _matmul_ue8m0(A, B, As, Bs, block_size, output_dtype) -> Optional[torch.Tensor]:
+    """Both scale tensors packed power-of-two exponents (``[rows, ceil(K/512)]`` int32, the row index
+    contiguous: what ``per_token_group_quant_fp8(scale_ue8m0=True)`` and ``transform_scale_ue8m0`` produce):
+    the block-scaled tensor-core kernel, which applies the scales inside the MMA and keeps the accumulator in
+    tensor memory for the whole K loop. Returns None when the layout or size is outside that kernel and the
+    caller unpacks to fp32 instead (same result up to the fp32 summation order)."""
+    if list(block_size) != [128, 128] or A.dim() != 2 or not A.is_cuda or N.get_tuning("gemm_ue8m0") == 0:
+        return None
+    M, K = A.shape
+    Nn = B.shape[0]
+    groups = (K + 511) // 512
+    if M < UE8M0_MIN_M or K % 16 or Nn % 8 or not (A.is_contiguous() and B.is_contiguous()) or B.shape[1] != K:
+        return None
+    if A.dtype != fp8_dtype or B.dtype != fp8_dtype or output_dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        return None
+
+    def mn_major(s, rows):
+        return (s.dim() == 2 and s.shape[0] == rows and s.shape[1] >= groups
+                and (s.stride(0) == 1 or rows == 1) and (s.shape[1] == 1 or s.stride(1) >= rows))
+
+    if not mn_major(As, M):
+        return None
+    if mn_major(Bs, Nn):
+        rows_per_word = 1
+    elif mn_major(Bs, (Nn + 127) // 128):
+        rows_per_word = 128
+    else:
+        return None
+    sfa_ld = As.stride(1) if As.shape[1] > 1 else max(As.shape[0], 1)
+    sfb_ld = Bs.stride(1) if Bs.shape[1] > 1 else max(Bs.shape[0], 1)
+    C = torch.empty(M, Nn, dtype=output_dtype, device=A.device)
+    with N.on_device(A):
+        st = N.load().b200_w8a8_block_fp8_gemm_ue8m0(
+            N.ptr(A), N.ptr(As), sfa_ld, N.ptr(B), N.ptr(Bs), sfb_ld, rows_per_word, N.ptr(C),
+            N.DTYPE_CODE[output_dtype], M, Nn, K, N.current_stream(),
+        )
+    N.check(st, "w8a8_block_fp8_matmul (UE8M0)")
+    return C
+
+
 def w8a8_block_fp8_matmul(
     A: torch.Tensor,
     B: torch.Tensor,
@@ -233,6 +276,10 @@ def w8a8_block_fp8_matmul(
     FP8 E4M3, contiguous; ``As [.., ceil(K/128)]`` fp32 with any strides (row- or
     column-major); ``Bs [ceil(N/128), ceil(K/128)]`` fp32. Only ``block_size == [128, 128]``.
     """
+    if As.dtype == torch.int32 and Bs.dtype == torch.int32:
+        C = _matmul_ue8m0(A, B, As, Bs, block_size, output_dtype)
+        if C is not None:
+            return C
     if As.dtype == torch.int32 or Bs.dtype == torch.int32:
         # power-of-two scales packed as exponent bytes: unpack to fp32 (exact) as the reference does
         # for its Triton path (fp8_utils.py:699-756)
