@@ -40,7 +40,8 @@ def _worker(rank, world, port, results):
         res["col_gather"] = O.rel_frobenius(colg(x.cuda()).float().cpu(), h_ref.float())
 
         # ---- MoE: TP over I, standard EP, all-to-all EP
-        T, E, topk, H, I = 64, 8, 2, 512, 512
+        # the intermediate size must split into whole 128-wide blocks per rank, the experts into whole experts
+        T, E, topk, H, I = 64, 8, 2, 512, max(512, 128 * world)
         g = torch.Generator().manual_seed(7)
         xm = torch.randn(T, H, generator=g).bfloat16()
         w1 = torch.stack([make_weight(2 * I, H, 10 + e)[0] for e in range(E)])
