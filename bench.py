@@ -1069,8 +1069,12 @@ def main():
     # output columns of a column-parallel layer, rows [rank*M/p, ..) of a row-parallel layer's summed result
     # (every rank holds the whole sum). The copies run on their own streams so that H2D, kernels and D2H of
     # consecutive layers overlap; every byte still crosses inside the timed region.
-    acts_host = {name: x.cpu().pin_memory() for name, _, _, _, x, _, _ in tp.layers}
     rows_lo, rows_hi = rank * M_ROWS // world, (rank + 1) * M_ROWS // world
+    # The batch lives in host memory once: a rank copies its own K shard of a row-parallel layer's input, and of a
+    # column-parallel layer's input (which every rank needs in full) only rows [rank*M/p, ..); the group then
+    # all-gathers those rows over NVLink instead of every rank pulling the whole matrix over PCIe.
+    acts_host = {name: (x[rows_lo:rows_hi] if (kind == "column" and world > 1) else x).cpu().pin_memory()
+                 for name, _, _, kind, x, _, _ in tp.layers}
     outs_host = {}
     for name, n, k, kind, *_ in tp.layers:
         shape = (M_ROWS, n // world) if kind == "column" else (rows_hi - rows_lo, n)
@@ -1079,7 +1083,9 @@ def main():
     d2h = sum(x.numel() * x.element_size() for x in outs_host.values())
     main_s = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    dev_in = {name: [torch.empty_like(x) for _ in range(2)] for name, _, _, _, x, _, _ in tp.layers}
+    dev_in = {name: [torch.empty(acts_host[name].shape, dtype=x.dtype, device=device) for _ in range(2)]
+              for name, _, _, _, x, _, _ in tp.layers}
+    gathered = {name: torch.empty_like(x) for name, _, _, kind, x, _, _ in tp.layers if kind == "column" and world > 1}
     consumed = {name: [None, None] for name, *_ in tp.layers}
     copied_out = {name: None for name, *_ in tp.layers}
     step_no = [0]
@@ -1097,6 +1103,9 @@ def main():
                 arrived = torch.cuda.Event()
                 arrived.record(s_in)
             main_s.wait_event(arrived)
+            if name in gathered:
+                torch.distributed.all_gather_into_tensor(gathered[name], buf)
+                buf = gathered[name]
             q, sc = S.per_token_group_quant_fp8(buf, 128, column_major_scales=True)
             if kind == "row" and world > 1:
                 # the summed result is a view of the symmetric buffer, rewritten by this layer's next call:
@@ -1140,7 +1149,8 @@ def main():
     e2e = {"value": M_ROWS * FLOPS_PER_ROW / e2e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
            "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms, "steps": e2e_steps, "passes_per_step": 1,
            "device_status_clear": e2e_ok,
-           "overlap": "H2D, kernels and D2H of consecutive layers run on three streams; every copy is inside the timed region"}
+           "overlap": "H2D, kernels and D2H of consecutive layers run on three streams; every copy is inside the timed region"
+                      + ("; a column-parallel layer's input is copied once over the group (1/p of its rows per rank) and all-gathered over NVLink" if world > 1 else "")}
     del dev_in, acts_host, outs_host
 
     line = {

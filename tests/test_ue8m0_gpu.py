@@ -137,7 +137,7 @@ def test_gemm_on_packed_power_of_two_scales():
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 224, 128), (130, 448, 512), (300, 1024, 640), (1024, 4096, 2048),
-                                   (257, 232, 4096 + 128), (4096, 7168, 2048), (65, 8, 16)])
+                                   (257, 232, 4096 + 128), (4096, 7168, 2048), (65, 8, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_block_scaled_kernel_shapes(M, N, K, out_dtype):
     """The block-scaled kernel on ragged and multi-tile shapes (tiles are 128 x 224; scales refresh every four
