@@ -171,43 +171,6 @@ int b200_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel
                               void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * w8a8_block_fp8_matmul with power-of-two (UE8M0) scales applied inside the tensor core
- * replaces: the DeepGEMM path the reference takes on Blackwell for block-FP8 linears
- *           (python/sglang/srt/layers/quantization/fp8_utils.py:466-540 deepgemm_w8a8_block_fp8_linear_with_fallback,
- *            scales prepared by :1209-1334 requant_weight_ue8m0 / transform_scale_ue8m0 and the
- *            scale_ue8m0 form of per_token_group_quant_fp8, fp8_kernel.py:498-610)
- * C[m,n] = sum_k A[m,k] * B[n,k] * 2^(ea[m,k/128]-127) * 2^(eb[n,k/128]-127), fp32 accumulation over the whole
- * K in tensor memory (tcgen05.mma.kind::mxf8f6f4.block_scale): no per-K-block promotion.
- * A [M,K] e4m3 row-major, B [N,K] e4m3 row-major. sfa: int32 words, word [g*sfa_ld + m] holds the exponent
- * bytes of row m for the 128-K blocks 4g..4g+3 (byte kb%4; the packed MN-major layout of the reference,
- * sfa_ld = rows padded to a multiple of 4). sfb: the same for the rows of B (sfb_rows_per_word = 1) or for its
- * 128-row blocks (sfb_rows_per_word = 128). C [M,N] bf16/f16/f32. K % 16 == 0, N % 8 == 0; no workspace. */
-int b200_w8a8_block_fp8_gemm_ue8m0(const void* A, const int32_t* sfa, int64_t sfa_ld, const void* B,
-                                   const int32_t* sfb, int64_t sfb_ld, int sfb_rows_per_word, void* C,
-                                   int c_dtype, int64_t M, int64_t N, int64_t K, void* stream);
-
-/* ---------------------------------------------------------------------------------------
- * w8a8_block_fp8_linear at decode size: quantise + GEMM + split-K sum in ONE launch
- * replaces: the composition of python/sglang/srt/layers/quantization/fp8_utils.py:814-834
- *           (per_token_group_quant_fp8, then w8a8_block_fp8_matmul) for M <= 16 rows; the
- *           reference chains its quantiser and GEMM as programmatic dependents instead
- *           (sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:456-466)
- * out[m,n] = sum_kb (q(x)[m,kb] . B[n,kb]) * xs[m,kb] * Bs[n/128,kb] with q / xs the 1x128 group
- * quantisation of x (arithmetic variant 0, eps as given): the same bytes and scales the stand-alone
- * quantiser produces, so the result equals quantise-then-GEMM up to the fp32 summation order.
- * x [M,K] bf16/f16 row-major (M <= 16), B [N,K] e4m3, Bs fp32 [ceil(N/128), ceil(K/128)],
- * out [M,N] in the dtype of x. K % 16 == 0, N % 8 == 0, N <= 524288.
- * workspace: b200_w8a8_block_fp8_linear_decode_workspace_bytes(M,N,K) bytes (fp32 partials of the K
- * splits). tickets: 4096 uint32 that are ZERO before the first call and belong to one stream (every
- * call leaves them zero; calls that overlap on the GPU must not share them). Anything else:
- * B200_E_UNSUPPORTED (callers fall back to the two-step path). */
-size_t b200_w8a8_block_fp8_linear_decode_workspace_bytes(int64_t M, int64_t N, int64_t K);
-int b200_w8a8_block_fp8_linear_decode(const void* x, int x_dtype, const void* B, const float* Bs,
-                                      void* out, int64_t M, int64_t N, int64_t K, float eps,
-                                      void* workspace, size_t workspace_bytes, void* tickets,
-                                      void* stream);
-
-/* ---------------------------------------------------------------------------------------
  * moe_align_block_size without a workspace (no counterpart in the reference).
  * For callers that cannot allocate device memory at the point of the call -- a host that may
  * not call cudaMalloc (e.g. inside a region where the allocator is frozen, or an embedding
