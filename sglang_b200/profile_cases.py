@@ -1,6 +1,8 @@
 """Small fixed workloads for profiling one kernel at a time (the commands quoted in ``profiles/``).
 
     python -m sglang_b200.profile_cases gemm M N K [calls]
+    python -m sglang_b200.profile_cases gemm_ue8m0 M N K [calls]          (packed power-of-two scales: block-scaled kernel)
+    python -m sglang_b200.profile_cases linear_decode M N K [calls]       (one-launch quantise + GEMM + split-K sum)
     python -m sglang_b200.profile_cases quant M K [calls]
     python -m sglang_b200.profile_cases align T topk E [calls]
     python -m sglang_b200.profile_cases route T E topk grouped|softmax [calls]
@@ -39,6 +41,28 @@ def main(argv) -> int:
         Bs = torch.rand((Nn + 127) // 128, (K + 127) // 128, device=dev, generator=g)
         for _ in range(calls(3)):
             out = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.bfloat16)
+    elif case == "gemm_ue8m0":
+        from sglang_b200 import weight_quant
+
+        M, Nn, K = (int(a) for a in args[:3])
+        x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(Nn, K, device=dev, generator=g) * 0.05).bfloat16()
+        A, As = S.per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+        B, Bs_f = weight_quant.quant_weight_ue8m0(w)
+        Bs = weight_quant.transform_scale_ue8m0(Bs_f, mn=Nn)
+        del x, w
+        for _ in range(calls(3)):
+            out = S.w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.bfloat16)
+    elif case == "linear_decode":
+        from sglang_b200 import fp8_kernel
+
+        M, Nn, K = (int(a) for a in args[:3])
+        x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+        B = torch.randn(Nn, K, device=dev, generator=g).to(fp8)
+        Bs = torch.rand((Nn + 127) // 128, (K + 127) // 128, device=dev, generator=g) * 1e-2
+        for _ in range(calls(3)):
+            out = fp8_kernel._linear_decode_fused(x, B, [128, 128], Bs, max_rows=16)
+            assert out is not None, "shape outside the one-launch kernel"
     elif case == "quant":
         M, K = (int(a) for a in args[:2])
         x = torch.randn(M, K, device=dev, generator=g).bfloat16()
