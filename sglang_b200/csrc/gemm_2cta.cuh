@@ -161,7 +161,7 @@ block_fp8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
       bool ok = true;
       for (int t = pair; t < total_tiles && ok; t += npairs) {
         int mt2, nt;
-        tile_coords(t, m_tiles2, p.n_tiles, p.group_m, mt2, nt);
+        tile_coords(t, m_tiles2, p.n_tiles, p.group_m, p.per_group_div, mt2, nt);
         const int a_row = mt2 * 2 * kBM + (int)rank * kBM;
         const int b_row = nt * BN + (int)rank * 128;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -220,7 +220,7 @@ block_fp8_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
     auto setup = [&](int t, Item& c) -> bool {
       if (t >= total_tiles) return false;
       c.t = t;
-      tile_coords(t, m_tiles2, p.n_tiles, p.group_m, c.mt2, c.nt);
+      tile_coords(t, m_tiles2, p.n_tiles, p.group_m, p.per_group_div, c.mt2, c.nt);
       c.row = c.mt2 * 2 * kBM + (int)rank * kBM + row_in_tile;
       c.col0 = c.nt * BN + half * 128;
       c.row_ok = c.row < p.M;
@@ -332,6 +332,8 @@ inline int launch_gemm_2cta(const void* A, const void* B, GemmParams p, cudaStre
   p.group_m = 8;  // 8 pair-tiles = 2048 rows swept per column tile
   p.k_splits = 1;
   p.kb_per_split = p.num_kb;
+  p.per_group_div = make_fastdiv(p.group_m * p.n_tiles);
+  p.k_splits_div = make_fastdiv(1);
   p.status = device_status_word();
   if (!p.status) {
     set_error_detail("cannot resolve the device status word");

@@ -168,6 +168,8 @@ inline int launch_gemm(const void* A, const void* B, int64_t b_rows_total, GemmP
   p.group_m = 16;
   p.k_splits = k_splits < 1 ? 1 : k_splits;
   p.kb_per_split = (int)cdiv(p.num_kb, p.k_splits);
+  p.per_group_div = make_fastdiv(p.group_m * p.n_tiles);
+  p.k_splits_div = make_fastdiv(p.k_splits);
   const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
   if (tiles == 0) return B200_OK;
   const int grid = (int)(tiles < sms ? tiles : sms);

@@ -31,6 +31,26 @@ namespace b200 {
 
 enum { GEMM_DENSE = 0, GEMM_GROUPED_SILU_QUANT = 1, GEMM_GROUPED_SCATTER = 2 };
 
+// Division by a divisor fixed at launch as a multiply-high and a shift (exact for 0 <= n < 2^31): the 32-bit
+// integer division of the hardware is a ~25-instruction dependent chain, and three of them in a row sat on the
+// critical path between two tiles of the promotion warps.
+struct FastDiv {
+  uint32_t mul, shr;
+};
+inline FastDiv make_fastdiv(int d) {
+  FastDiv f = {0u, 0u};
+  if (d <= 1) return f;  // mul == 0 marks "divide by one"
+  int l = 0;
+  while ((1ll << l) < d) ++l;  // ceil(log2 d)
+  const int p = 31 + l;
+  f.mul = (uint32_t)(((1ull << p) + (uint64_t)d - 1) / (uint64_t)d);
+  f.shr = (uint32_t)(p - 32);
+  return f;
+}
+__device__ __forceinline__ int fast_div(int n, FastDiv f) {
+  return f.mul == 0u ? n : (int)(__umulhi((uint32_t)n, f.mul) >> f.shr);
+}
+
 struct GemmParams {
   const float* As;  // A scales: As[m*as_sm + kb*as_sk]
   int64_t as_sm, as_sk;
@@ -42,7 +62,8 @@ struct GemmParams {
   int n_blocks;    // ceil(N/128): rows of Bs per expert
   int n_tiles;     // ceil(N/BN)
   int m_tiles;     // ceil(M/128) (grouped: upper bound; the live count is read on device)
-  int group_m;     // tiles of M swept together for L2 reuse
+  int group_m;     // tiles of M swept together for L2 reuse (a power of two)
+  FastDiv per_group_div, k_splits_div;  // division by group_m * n_tiles and by k_splits
   // split-K (dense, small problems): work item = (tile, split); split s covers K blocks
   // [s*kb_per_split, ...) and writes an fp32 partial at C + s*split_stride
   int k_splits, kb_per_split;
@@ -194,15 +215,17 @@ __device__ __forceinline__ void promote32(float* acc, const uint32_t (&v)[32], f
 }
 
 // tile index -> (m_tile, n_tile): sweep group_m row-tiles for every column tile before moving
-// on, so the CTAs running together share A rows and B columns in L2.
-__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mt, int& nt) {
+// on, so the CTAs running together share A rows and B columns in L2. group_m is a power of two;
+// only the last, shorter group of row tiles pays for a real division.
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, FastDiv per_group_div,
+                                            int& mt, int& nt) {
   const int per_group = group_m * n_tiles;
-  const int g = t / per_group;
+  const int g = fast_div(t, per_group_div);
   const int first_m = g * group_m;
   const int rows = min(group_m, m_tiles - first_m);
   const int r = t - g * per_group;
-  mt = first_m + r % rows;
-  nt = r / rows;
+  nt = rows == group_m ? r >> (31 - __clz(group_m)) : r / rows;
+  mt = first_m + r - nt * rows;
 }
 
 template <int BN, int MODE, typename OutT, int FAN = 1>
@@ -276,10 +299,10 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t it = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const int t = item / S_k, ks = item - t * S_k;
+      const int t = fast_div(item, p.k_splits_div), ks = item - t * S_k;
       const int kb0 = ks * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
       int mt, nt;
-      tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
+      tile_coords(t, m_tiles, p.n_tiles, p.group_m, p.per_group_div, mt, nt);
       int b_row = nt * BN, b_row2 = 0;
       if (MODE != GEMM_DENSE) {
         const int e = p.expert_ids[mt];
@@ -318,10 +341,10 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t it = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const int t = item / S_k, ks = item - t * S_k;
+      const int t = fast_div(item, p.k_splits_div), ks = item - t * S_k;
       const int kb0 = ks * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
       int mt, nt;
-      tile_coords(t, m_tiles, p.n_tiles, p.group_m, mt, nt);
+      tile_coords(t, m_tiles, p.n_tiles, p.group_m, p.per_group_div, mt, nt);
       if (MODE != GEMM_DENSE && p.expert_ids[mt] < 0) continue;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % S, b = it & 1;
@@ -367,11 +390,11 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     };
     auto setup = [&](int item, Item& c) -> bool {
       for (; item < total_items; item += gridDim.x) {
-        const int t = item / S_k;
+        const int t = fast_div(item, p.k_splits_div);
         c.ks = item - t * S_k;
         c.kb0 = c.ks * p.kb_per_split;
         c.kb1 = min(num_kb, c.kb0 + p.kb_per_split);
-        tile_coords(t, m_tiles, p.n_tiles, p.group_m, c.mt, c.nt);
+        tile_coords(t, m_tiles, p.n_tiles, p.group_m, p.per_group_div, c.mt, c.nt);
         c.expert = 0;
         if (MODE != GEMM_DENSE) {
           c.expert = p.expert_ids[c.mt];
@@ -436,14 +459,16 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           ok = ptx::mbar_wait(tfull_bar(b), (it >> 1) & 1, abort_flag);
           if (!ok) break;
-          // the MMAs of this K block have completed, so they have also finished reading their
-          // shared-memory stage: hand it back to the TMA producer
-          if (warp == 0 && lane == 0) ptx::mbar_arrive(empty_bar(it % S));
           ptx::tc_fence_after();
           const uint32_t ta = lane_base + b * BN;
           uint32_t va[32], vb[32];
           // one TMEM load in flight behind the FMAs of the previous 32 columns
           ptx::tmem_ld32(ta, va);
+          // The MMAs of this K block have completed, so they have also finished reading their
+          // shared-memory stage: hand it back to the TMA producer. Done behind the first TMEM load: the
+          // accumulator buffer goes back to the MMA warp only when the slowest of the eight warps has read
+          // it, and this arrival in front of the load made warp 0 that warp by about 120 cycles per K block.
+          if (warp == 0 && lane == 0) ptx::mbar_arrive(empty_bar(it % S));
           ptx::tmem_ld_wait(va);
           ptx::tmem_ld32(ta + 32, vb);
           promote32(acc, va, sc);
@@ -481,7 +506,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       };
       if (L::kStaged) {
         // the bulk stores of the previous tile must have read the staging area before it is rewritten
-        if (MODE != GEMM_GROUPED_SCATTER && lane == 0) ptx::tma_store_wait_read();
+        if (MODE != GEMM_GROUPED_SCATTER && lane < L::kBoxesPerWarp) ptx::tma_store_wait_read();
         __syncwarp();
         if (MODE == GEMM_GROUPED_SILU_QUANT) named_bar_sync(2 + quarter, 64);  // the box is shared with warp ^ 4
       }
@@ -539,11 +564,12 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (MODE == GEMM_DENSE) {
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
+            // one lane per box: the issue cost of a bulk tensor store (several hundred cycles on the thread
+            // that issues it) is paid once per warp instead of once per box
+            if (lane < L::kBoxesPerWarp) {
               constexpr int kColsPerBox = 128 / (int)sizeof(OutT);
-#pragma unroll
-              for (int bxi = 0; bxi < L::kBoxesPerWarp; ++bxi) {
-                const int bx = bxi;
+              {
+                const int bx = lane;
                 if (col0 + bx * kColsPerBox < p.N) {
                   if (FAN == 1) {
                     ptx::tma_store_3d(&tmap_c, wstage + bx * 4096, col0 + bx * kColsPerBox, cur.mt * kBM + quarter * 32, ks);
@@ -606,7 +632,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   }
 
   // every bulk store of this CTA must have completed before its shared memory is released
-  if (L::kStaged && MODE != GEMM_GROUPED_SCATTER && warp < Cfg::kEpiWarps && lane == 0) ptx::tma_store_wait_all();
+  if (L::kStaged && MODE != GEMM_GROUPED_SCATTER && warp < Cfg::kEpiWarps && lane < L::kBoxesPerWarp) ptx::tma_store_wait_all();
 
   // ---------------------------------------------------------------------- teardown
   if (*abort_flag) {

@@ -34,6 +34,7 @@ struct Ue8m0Params {
   int sfb_rows_per_word;  // 1: one word per row of B; 128: one word per 128-row block
   void* C;
   int M, N, K, num_kb, m_tiles, n_tiles, group_m;
+  FastDiv per_group_div;  // division by group_m * n_tiles
   int* status;
 };
 
@@ -146,7 +147,7 @@ block_fp8_gemm_ue8m0_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int mt, nt;
-      tile_coords(t, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
+      tile_coords(t, p.m_tiles, p.n_tiles, p.group_m, p.per_group_div, mt, nt);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % S;
         ok = ptx::mbar_wait(empty_bar(s), ((it / S) & 1) ^ 1, abort_flag);
@@ -168,7 +169,7 @@ block_fp8_gemm_ue8m0_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int mt, nt;
-      tile_coords(t, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
+      tile_coords(t, p.m_tiles, p.n_tiles, p.group_m, p.per_group_div, mt, nt);
       const int m0 = mt * kBM, n0 = nt * BN;
       for (int g = 0; g < groups; ++g, ++gi) {
         const int slot = gi % SFS;
@@ -251,7 +252,7 @@ block_fp8_gemm_ue8m0_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
       int mt, nt;
-      tile_coords(t, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
+      tile_coords(t, p.m_tiles, p.n_tiles, p.group_m, p.per_group_div, mt, nt);
       const int as = tile_no & 1;
       ok = ptx::mbar_wait(acc_full_bar(as), (tile_no >> 1) & 1, abort_flag);
       if (!ok) break;
@@ -298,6 +299,7 @@ inline int launch_gemm_ue8m0(const void* A, const void* B, Ue8m0Params p, cudaSt
   p.m_tiles = (int)cdiv(p.M, kBM);
   p.n_tiles = (int)cdiv(p.N, Ue8m0Cfg::BN);
   p.group_m = 16;
+  p.per_group_div = make_fastdiv(p.group_m * p.n_tiles);
   p.status = device_status_word();
   if (!p.status) {
     set_error_detail("cannot resolve the device status word");
