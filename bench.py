@@ -642,7 +642,72 @@ def bench_comparators(S, device):
         out[label] = item
         del x, wq, ws, q, s, ours
     torch.cuda.empty_cache()
+    try:
+        out["llama70b_sustained"] = sustained_comparison(S, device, fi_mod, fi_ws if fi_mod is not None else None)
+    except Exception as e:
+        out["llama70b_sustained"] = {"error": repr(e)[:300]}
+        torch.cuda.synchronize()
+    torch.cuda.empty_cache()
     return out
+
+
+def sustained_comparison(S, device, fi_mod, fi_ws, seconds: float = 1.5):
+    """The four Llama-3-70B GEMMs (M = 4096) looped for ``seconds`` under the power cap, GEMMs only: this
+    library's promotion kernel (fp32 scales), its block-scaled kernel (the same layers re-quantised to
+    power-of-two scales) and FlashInfer's sm100 kernel (fp32 scales). TF/s over the whole loop, with the clock
+    record of each loop; the burst figures above are single graph replays at full clock."""
+    from sglang_b200 import synthetic, weight_quant as W
+
+    ops = []
+    for i, (name, n, k, _) in enumerate(TP_LINEARS):
+        g = torch.Generator(device=device).manual_seed(8200 + i)
+        x = torch.randn(M_ROWS, k, device=device, generator=g).bfloat16()
+        w = (torch.randn(n, k, device=device, generator=g) * 0.02).bfloat16()
+        wq, ws = synthetic.block_quant_weight_fp8(w)
+        q, s = S.per_token_group_quant_fp8(x, 128, column_major_scales=True)
+        wq2, ws2 = W.quant_weight_ue8m0(w)
+        ws2p = W.transform_scale_ue8m0(ws2, mn=n)
+        q2, s2 = S.per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)
+        o = torch.empty(M_ROWS, n, dtype=torch.bfloat16, device=device)
+        ops.append((q, s, wq, ws, q2, s2, wq2, ws2p, s.t().contiguous(), ws.t().contiguous(), o))
+        del x, w
+    flops = sum(2.0 * M_ROWS * n * k for _, n, k, _ in TP_LINEARS)
+
+    def promo():
+        for q, s, wq, ws, *_ in ops:
+            S.w8a8_block_fp8_matmul(q, wq, s, ws, [128, 128], torch.bfloat16)
+
+    def scaled():
+        for _, _, _, _, q2, s2, wq2, ws2p, *_ in ops:
+            S.w8a8_block_fp8_matmul(q2, wq2, s2, ws2p, [128, 128], torch.bfloat16)
+
+    def fi():
+        for q, _, wq, _, _, _, _, _, a_sc, b_sc, o in ops:
+            fi_mod.gemm_fp8_nt_groupwise(fi_ws, q, wq, a_sc, b_sc, o, 1, 128, 128, "MN", 1)
+
+    res = {"seconds_target": seconds, "rows": M_ROWS}
+    arms = [("ours_fp32_scales_promotion", promo), ("ours_ue8m0_block_scaled_mma", scaled)]
+    if fi_mod is not None:
+        arms.append(("flashinfer_cutlass_sm100_1sm", fi))
+    for label, fn in arms:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        reps = max(4, int(seconds * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+        with ClockSampler(torch.cuda.current_device()) as cs:
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        res[label] = {"tflops": flops * reps / ms / 1e9, "passes": reps, "seconds": ms / 1e3, "clocks": cs.summary()}
+    return res
 
 
 def bench_kernels(S, device):
