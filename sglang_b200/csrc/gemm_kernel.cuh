@@ -117,10 +117,12 @@ struct GemmCfg {
 };
 
 // Shared-memory plan of one instantiation. The promotion warps stage their part of the output
-// tile (32 rows x 128 columns per warp) in shared memory in the TMA 128-byte-swizzled box layout
-// and write it out with bulk tensor stores (dense, gate_up) or with row-contiguous 16-byte
-// stores (scatter): a thread owns a whole row, so direct stores would touch 32 different rows
-// per instruction. Staging is used by the 256-wide tile with 16-bit / FP8 output (the shapes
+// tile (32 rows x 128 columns per warp) in shared memory and write it out asynchronously: in the
+// TMA 128-byte-swizzled box layout with bulk tensor stores (dense, gate_up), or (scatter) row-major
+// with a 16-byte pad per row -- conflict-free for one 16-byte chunk per lane -- and one untiled bulk
+// copy per row, issued by the lane that owns the row. A thread owns a whole row, so direct stores
+// would touch 32 different rows per instruction, and plain stores out of the staging area stall the
+// promotion warps while 64 KB per tile drain through the store queue. Staging is used by the 256-wide tile with 16-bit / FP8 output (the shapes
 // where the epilogue is on the critical path); fp32 output and the 128-wide tile (small
 // problems, split-K partials) keep direct row stores.
 template <int BN, int MODE, typename OutT>
@@ -129,7 +131,8 @@ struct GemmLayout {
   static constexpr int kRowBytes = MODE == GEMM_GROUPED_SILU_QUANT ? 128 : 128 * (int)sizeof(OutT);  // per thread
   static constexpr bool kStaged = BN == 256 && kRowBytes <= 256;
   static constexpr int kBoxesPerWarp = kRowBytes / 128;     // boxes of 32 rows x 128 bytes
-  static constexpr int kWarpStageBytes = 32 * kRowBytes;    // 4, 8 or 16 KB
+  static constexpr int kRowStride = MODE == GEMM_GROUPED_SCATTER ? kRowBytes + 16 : kRowBytes;  // scatter: padded rows
+  static constexpr int kWarpStageBytes = 32 * kRowStride;   // 4, 8 or 16 KB (+ 512 B of padding)
   static constexpr int kStoreWarps = MODE == GEMM_GROUPED_SILU_QUANT ? 4 : Cfg::kEpiWarps;
   static constexpr int kStagingBytes =
       (MODE == GEMM_GROUPED_SILU_QUANT ? Cfg::kExchangeBytes : 0) + (kStaged ? kStoreWarps * kWarpStageBytes : 0);
@@ -144,10 +147,14 @@ struct GemmLayout {
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-// silu(g) * u with the fast exponential / reciprocal (relative error ~1e-6: far below the
-// FP8 quantisation step that follows).
+// silu(g) * u = g * u * (0.5 + 0.5 * tanh(g / 2)) with the hardware tanh: one special-function
+// instruction per element instead of an exponential and a reciprocal (the special-function unit issues
+// a warp instruction every 8 cycles and was half of this epilogue). Relative error of tanh.approx.f32
+// about 2^-11: far below the FP8 quantisation step (2^-4) that follows.
 __device__ __forceinline__ float silu_mul_fast(float g, float u) {
-  return __fdividef(g, 1.0f + __expf(-g)) * u;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * g));
+  return (g * u) * fmaf(0.5f, t, 0.5f);
 }
 
 // eight floats -> eight 16-bit values in one 16-byte register quad
@@ -388,7 +395,9 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const float* bs2_ptr;  // MODE 1: scales of the up rows (b_pf/bs_ptr are the gate rows')
       float b2_pf[4];
     };
-    auto setup = [&](int item, Item& c) -> bool {
+    // hint: the expert of work item `hint_item`, requested at the start of the previous tile so that the
+    // dependent chain "expert id -> scale rows" does not start with an L2 round trip between two tiles
+    auto setup = [&](int item, Item& c, int hint_item, int hint_expert) -> bool {
       for (; item < total_items; item += gridDim.x) {
         const int t = fast_div(item, p.k_splits_div);
         c.ks = item - t * S_k;
@@ -397,7 +406,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tile_coords(t, m_tiles, p.n_tiles, p.group_m, p.per_group_div, c.mt, c.nt);
         c.expert = 0;
         if (MODE != GEMM_DENSE) {
-          c.expert = p.expert_ids[c.mt];
+          c.expert = item == hint_item ? hint_expert : p.expert_ids[c.mt];
           if (c.expert < 0) continue;  // rows of experts that live on another rank
         }
         c.item = item;
@@ -428,8 +437,16 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t it = 0;
     bool ok = true;
     Item cur;
-    bool have = setup(blockIdx.x, cur);
+    bool have = setup(blockIdx.x, cur, -1, 0);
     while (have) {
+      // expert of the next work item of this CTA: in flight during the whole K loop
+      int hint_expert = 0;
+      const int hint_item = cur.item + gridDim.x;
+      if (MODE != GEMM_DENSE && hint_item < total_items) {
+        int hmt, hnt;
+        tile_coords(fast_div(hint_item, p.k_splits_div), m_tiles, p.n_tiles, p.group_m, p.per_group_div, hmt, hnt);
+        hint_expert = __ldg(p.expert_ids + hmt);
+      }
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
@@ -490,7 +507,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       if (!ok) break;
 
       Item nxt;
-      const bool have_next = setup(cur.item + gridDim.x, nxt);
+      const bool have_next = setup(cur.item + gridDim.x, nxt, hint_item, hint_expert);
 
       // ------------------------------------------------------------ tile epilogue
       const int row = cur.row, col0 = cur.col0, nt = cur.nt, ks = cur.ks;
@@ -500,13 +517,15 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const uint32_t wstage = staging + store_warp * L::kWarpStageBytes;
       // 16-byte chunk c of this thread's row (= lane) goes to box c/8, slot (c%8) ^ (lane%8)
       auto stage_chunk = [&](int c, uint4 v) {
-        const uint32_t addr = wstage + (c >> 3) * 4096 + lane * 128 + (((c & 7) ^ (lane & 7)) << 4);
+        const uint32_t addr = MODE == GEMM_GROUPED_SCATTER
+                                  ? wstage + lane * L::kRowStride + (c << 4)
+                                  : wstage + (c >> 3) * 4096 + lane * 128 + (((c & 7) ^ (lane & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                      : "memory");
       };
       if (L::kStaged) {
         // the bulk stores of the previous tile must have read the staging area before it is rewritten
-        if (MODE != GEMM_GROUPED_SCATTER && lane < L::kBoxesPerWarp) ptx::tma_store_wait_read();
+        if (MODE == GEMM_GROUPED_SCATTER || lane < L::kBoxesPerWarp) ptx::tma_store_wait_read();
         __syncwarp();
         if (MODE == GEMM_GROUPED_SILU_QUANT) named_bar_sync(2 + quarter, 64);  // the box is shared with warp ^ 4
       }
@@ -586,24 +605,15 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               ptx::tma_store_commit();
             }
           } else {
-            // scatter: rows go to arbitrary (token, slot) positions; write each row as one
-            // contiguous run of 16-byte chunks, kRowBytes / 16 lanes per row
-            __syncwarp();
-            constexpr int kLanesPerRow = L::kRowBytes / 16;     // 16 (16-bit) or 32 (fp32)
-            constexpr int kRowsPerIter = 32 / kLanesPerRow;
-            const int c = lane % kLanesPerRow;
-#pragma unroll
-            for (int i = 0; i < 32 / kRowsPerIter; ++i) {
-              const int r = i * kRowsPerIter + lane / kLanesPerRow;
-              const int dst_flat = __shfl_sync(0xffffffffu, flat, r);
-              const uint32_t addr = wstage + (c >> 3) * 4096 + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-              uint4 v;
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-              const int col = col0 + c * (16 / (int)sizeof(OutT));
-              if (dst_flat < p.numel && col < p.N)
-                *reinterpret_cast<uint4*>(static_cast<OutT*>(p.C) + (int64_t)dst_flat * p.ldc + col) = v;
+            // scatter: rows go to arbitrary (token, slot) positions; every lane sends its own staged row as
+            // one contiguous bulk copy (it reads only what this thread wrote: no warp barrier)
+            ptx::fence_proxy_async_smem();
+            const int cols = min(128, p.N - col0);  // N is a multiple of 8: whole 16-byte chunks
+            if (flat < p.numel && cols > 0) {
+              ptx::bulk_store_1d(static_cast<OutT*>(p.C) + (int64_t)flat * p.ldc + col0, wstage + lane * L::kRowStride,
+                                 (uint32_t)cols * (uint32_t)sizeof(OutT));
+              ptx::tma_store_commit();
             }
-            __syncwarp();  // staging area free for the next tile
           }
         } else {
           // fp32 output with 256-wide tiles: direct row stores
@@ -632,7 +642,7 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   }
 
   // every bulk store of this CTA must have completed before its shared memory is released
-  if (L::kStaged && MODE != GEMM_GROUPED_SCATTER && warp < Cfg::kEpiWarps && lane < L::kBoxesPerWarp) ptx::tma_store_wait_all();
+  if (L::kStaged && warp < Cfg::kEpiWarps && (MODE == GEMM_GROUPED_SCATTER || lane < L::kBoxesPerWarp)) ptx::tma_store_wait_all();
 
   // ---------------------------------------------------------------------- teardown
   if (*abort_flag) {
