@@ -86,10 +86,19 @@ __device__ __forceinline__ void write_block_outputs(const int* cnt, const int* s
                                                     int32_t* num_post_pad, int32_t* cumsum) {
   const int tid = threadIdx.x;
   const int total = start[B];
-  for (int b = tid; b < B; b += kAlignThreads) {
-    cumsum[b] = start[b] + cnt[b];
-    const int lo = start[b] / block_size, hi = (b + 1 < B ? start[b + 1] : total) / block_size;
-    for (int i = lo; i < hi && i < max_blocks; ++i) expert_ids[i] = b - 1;
+  for (int b = tid; b < B; b += kAlignThreads) cumsum[b] = start[b] + cnt[b];
+  // One thread per block (not per bucket: with expert parallelism the "not mine" bucket alone owns hundreds of
+  // blocks, which one thread used to write in a row): the bucket of block i is the last b with
+  // start[b] <= i * block_size; empty buckets share their start with the next one and are skipped by the search.
+  const int nblocks = (int)min((int64_t)(total / block_size), max_blocks);
+  for (int i = tid; i < nblocks; i += kAlignThreads) {
+    const int pos = i * block_size;
+    int lo = 0, hi = B;  // invariant: start[lo] <= pos < start[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (start[mid] <= pos) lo = mid; else hi = mid;
+    }
+    expert_ids[i] = lo - 1;
   }
   for (int64_t i = total / block_size + tid; i < max_blocks; i += kAlignThreads) expert_ids[i] = -1;
   if (tid == 0) {

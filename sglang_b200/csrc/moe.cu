@@ -118,35 +118,59 @@ __global__ void __launch_bounds__(256) moe_gather_fp8_kernel(
   }
 }
 
-// out[t, :] = scale * sum_j y[t*topk + j, :] over the slots whose expert id is valid.
+// out[t, :] = scale * sum_j y[t*topk + j, :] over the slots whose expert id is valid. One block per token: the
+// valid slots are listed once in shared memory, so a row none of whose slots is valid (most rows of an
+// expert-parallel receive area) costs one read of its ids, and there is no per-thread division. Four row loads
+// are in flight per thread and six blocks fit an SM; the sum stays in slot order.
+constexpr int kSumReduceMaxSlots = 64;
 template <typename T>
-__global__ void __launch_bounds__(256) moe_sum_reduce_kernel(const T* __restrict__ y, const int32_t* __restrict__ topk_ids,
-                                                             T* __restrict__ out, int64_t T_tokens, int topk, int E,
-                                                             int64_t H, float scale, int skip_unrouted) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int vec_per_row = (int)(H / 8);
-  if (c >= T_tokens * vec_per_row) return;
-  const int64_t t = c / vec_per_row;
-  const int v = (int)(c - t * vec_per_row);
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  bool any = false;
-  for (int j = 0; j < topk; ++j) {
-    const int e = topk_ids[t * topk + j];
-    if (e < 0 || e >= E) continue;
-    any = true;
-    const uint4 r = ld_nc_16(y + (t * topk + j) * H + v * 8);
-    const T* h = reinterpret_cast<const T*>(&r);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+__global__ void __launch_bounds__(256, 6) moe_sum_reduce_kernel(const T* __restrict__ y, const int32_t* __restrict__ topk_ids,
+                                                                T* __restrict__ out, int topk, int E, int64_t H, float scale,
+                                                                int skip_unrouted) {
+  __shared__ int s_slot[kSumReduceMaxSlots];
+  __shared__ int s_n;
+  const int64_t t = blockIdx.x;
+  if (threadIdx.x < 32) {  // warp 0 compacts the valid slots, ascending (topk <= 64: two rounds of 32)
+    int n = 0;
+    for (int j0 = 0; j0 < topk; j0 += 32) {
+      const int j = j0 + (int)threadIdx.x;
+      const int e = j < topk ? __ldg(topk_ids + t * topk + j) : -1;
+      const bool ok = e >= 0 && e < E;
+      const unsigned m = __ballot_sync(0xffffffffu, ok);
+      if (ok) s_slot[n + __popc(m & ((1u << threadIdx.x) - 1u))] = j;
+      n += __popc(m);
+    }
+    if (threadIdx.x == 0) s_n = n;
   }
-  if (!any && skip_unrouted) return;  // a row no local expert serves: nobody reads it
-  uint4 o;
-  T* oh = reinterpret_cast<T*>(&o);
+  __syncthreads();
+  const int n = s_n;
+  if (n == 0 && skip_unrouted) return;  // a row no local expert serves: nobody reads it
+  const int vec_per_row = (int)(H / 8);
+  const T* base = y + t * topk * H;
+  for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+    float acc[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * scale);
-  *reinterpret_cast<uint4*>(out + t * H + v * 8) = o;
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int k0 = 0; k0 < n; k0 += 4) {
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k0 + k < n) r[k] = ld_nc_16(base + (int64_t)s_slot[k0 + k] * H + v * 8);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (k0 + k < n) {
+          const T* h = reinterpret_cast<const T*>(&r[k]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += to_f32<T>(h[i]);
+        }
+      }
+    }
+    uint4 o;
+    T* oh = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) oh[i] = from_f32<T>(acc[i] * scale);
+    *reinterpret_cast<uint4*>(out + t * H + v * 8) = o;
+  }
 }
 
 // Same reduction over fp32 split-K partials y[splits][rows * slots][H] of the down GEMM
@@ -410,9 +434,8 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   }
   if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, T>(aq2, w2, (int64_t)E * H, p, force_bn, st, tiles_hint))) return rc;
   if (!no_combine) {
-    const int64_t total = T_tokens * (H / 8);
-    moe_sum_reduce_kernel<T><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(c3, topk_ids, static_cast<T*>(out), T_tokens,
-                                                                        topk, E, H, routed_scale, skip_unrouted);
+    moe_sum_reduce_kernel<T><<<(unsigned)T_tokens, 256, 0, st>>>(c3, topk_ids, static_cast<T*>(out), topk, E, H,
+                                                                  routed_scale, skip_unrouted);
     if ((rc = check_launch("moe_sum_reduce"))) return rc;
   }
   return B200_OK;
@@ -538,6 +561,7 @@ extern "C" int b200_fused_experts_fp8(const void* hidden, const float* hidden_sc
                    (long long)H, (long long)I);
   B200_UNSUPPORTED(E + 1 > 1025, "fused_experts: more than 1024 experts");
   B200_UNSUPPORTED(T * topk >= (1LL << 30), "fused_experts: too many (token, slot) pairs");
+  B200_UNSUPPORTED(topk > kSumReduceMaxSlots, "fused_experts: more than %d experts per token", kSumReduceMaxSlots);
   B200_CHECK_ARG(!apply_router_weight_on_input || topk == 1, "apply_router_weight_on_input needs topk == 1");
   B200_CHECK_ARG(no_combine >= 0 && no_combine <= 2, "fused_experts: unknown combine mode %d", no_combine);
   B200_CHECK_ARG(((uintptr_t)hidden & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w1 & 15) == 0 &&
