@@ -68,6 +68,23 @@ def test_shapes_vs_fp32_oracle(T, E, topk, H, I):
     assert O.rel_frobenius(out.float().cpu(), ref) < TOL
 
 
+@pytest.mark.parametrize("T,E,topk", [(300, 48, 11), (260, 64, 40)])
+def test_many_experts_per_token_slot_sum(T, E, topk):
+    """More slots per token than one round of the slot sum takes (four loads per thread, 32 ids per ballot), with a
+    third of the ids belonging to another rank (-1): the sum visits exactly the valid slots, in order."""
+    H, I = 256, 128
+    g = torch.Generator().manual_seed(3 * T + topk)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1, w2, w1_s, w2_s = _weights(E, I, H, 11 + topk)
+    tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), topk, True)
+    ti = torch.where(torch.rand(T, topk, generator=g) < 0.33, torch.full_like(ti, -1), ti)
+    ti[0] = -1  # a token none of whose experts is local
+    ref = O.fused_experts_fp8(x, w1, w2, w1_s, w2_s, tw, ti, [128, 128])
+    out = _run(x, w1, w2, w1_s, w2_s, tw, ti)
+    assert O.rel_frobenius(out.float().cpu(), ref) < TOL
+    assert float(out[0].float().abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("T,E,topk,H,I", [(1, 8, 2, 256, 2048), (3, 8, 2, 512, 1024), (5, 16, 4, 256, 1536)])
 def test_few_tokens_split_k_down_gemm(T, E, topk, H, I):
     """A handful of tokens: the down GEMM splits K = I over the SMs and the slot reduction sums
