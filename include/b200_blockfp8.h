@@ -60,8 +60,10 @@ int b200_read_device_status(int* out, void* stream);
  * Product calls never read the environment; a knob left at -1 is decided automatically.
  * Names: "gemm_bn" (128 / 256), "gemm_skinny" (0 = never the decode kernel),
  * "gemm_skinny_max_m", "gemm_splitk" (> 0 forces the K split; size the workspace after setting
- * it), "gemm_2cta" (0 / 1), "moe_down_splitk" (0 = never), "moe_zero_pads" (0 / 1),
- * "peer_wait_ms" (limit of a device-side wait for another GPU, 100 .. 60000).
+ * it), "gemm_2cta" (0 / 1), "gemm_ue8m0" (0 = packed power-of-two scales are unpacked and take the
+ * fp32-scale kernels), "linear_decode_fused" (0 = never the one-launch decode linear), "moe_decode"
+ * (1 = few-token swapped-operand MoE kernels; default off), "moe_down_splitk" (0 = never),
+ * "moe_zero_pads" (0 / 1), "peer_wait_ms" (limit of a device-side wait for another GPU, 100 .. 60000).
  * No counterpart in the reference (its Triton launchers read tuned JSON configs instead,
  * python/sglang/srt/layers/moe/fused_moe_triton/fused_moe_triton_config.py). Not thread-safe
  * against concurrent launches: set knobs before the calls they affect. */
