@@ -350,6 +350,35 @@ int b200_peer_handshake(void* my_flags, void* const* peer_flags, int n_ranks, in
 int b200_ep_combine(void* const* peer_out, const int32_t* topk_ids, void* out, int dtype, int64_t T,
                     int64_t T_max, int topk, int64_t H, int E, int n_ranks, int rank, void* stream);
 
+/* Combine by push (the default of the Python layer): the owners' down GEMM sends every finished
+ * (token, slot) row straight into the SOURCE rank's own area while the remaining tiles are still
+ * being multiplied, so the combine traffic overlaps the GEMM instead of following it; after the
+ * second handshake the source sums its slots locally.
+ * replaces: the same DeepEP combine (deepep.py:560-602); in the reference the expert GEMMs and
+ *           the combine all-to-all are separate steps.
+ * b200_fused_experts_fp8_scatter: fused experts over T positions of quantised rows (hidden_q e4m3
+ *   [T,H], hidden_scale fp32 [T,H/128], topk_ids local to this rank, -1 = not mine), router weight
+ *   applied, no slot sum: the row of pair flat = t*topk + j goes to dests[flat / rows_per_dest] at
+ *   row flat % rows_per_dest of a [rows_per_dest, H] bf16/f16 buffer (HOST array of device
+ *   pointers, peer memory allowed; with the receive-area layout above rows_per_dest = T_max*topk and
+ *   the destination is the source rank of the token). Rows of pairs that are not this rank's are
+ *   not written. Workspace as b200_fused_experts_fp8.
+ * b200_moe_sum_reduce: out[t,:] = scale * sum over the slots j with 0 <= topk_ids[t,j] < E of
+ *   rows[t*topk + j, :], fp32 sum in slot order; rows without a valid id are zeroed, or left
+ *   unwritten with skip_unrouted. poison_on_status != 0: when the device status word is non-zero
+ *   (a handshake before it gave up) out is filled with NaN instead. The last step of
+ *   fused_experts (moe_sum_reduce, python/sglang/srt/layers/moe/moe_runner/triton_utils/fused_moe.py:726-745)
+ *   as an entry point of its own. */
+int b200_fused_experts_fp8_scatter(const void* hidden_q, const float* hidden_scale, int out_dtype,
+                                   const void* w1, const void* w2, const float* w1_scale,
+                                   const float* w2_scale, const float* topk_weights,
+                                   const int32_t* topk_ids, void* const* dests, int n_dest,
+                                   int64_t rows_per_dest, int64_t T, int topk, int E, int64_t H,
+                                   int64_t I, void* workspace, size_t workspace_bytes, void* stream);
+int b200_moe_sum_reduce(const void* rows, const int32_t* topk_ids, void* out, int dtype, int64_t T,
+                        int topk, int E, int64_t H, float scale, int skip_unrouted,
+                        int poison_on_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -92,6 +92,15 @@ SIGNATURES = {
         c_int,
         [POINTER(c_void_p), c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int, c_int, c_int, c_void_p],
     ),
+    "b200_fused_experts_fp8_scatter": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+         c_int64, c_int, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+    ),
+    "b200_moe_sum_reduce": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_float, c_int, c_int, c_void_p],
+    ),
     "b200_route_topk": (
         c_int,
         [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,

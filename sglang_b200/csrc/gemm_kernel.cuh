@@ -86,6 +86,11 @@ struct GemmParams {
   // sends the tile of row block mt only to dest[mt % n_dest] (its owner in a reduce-scatter).
   int n_dest, dest_by_tile;
   void* dest[8];
+  // Scatter mode over several buffers (expert-parallel combine by push): the row of pair `flat` goes to
+  // dest[flat / scatter_rows_per_dest], row flat % scatter_rows_per_dest -- the source rank's own
+  // [tokens x slots, N] area, possibly over NVLink. 0 = one buffer, C.
+  int scatter_rows_per_dest;
+  FastDiv scatter_div;
 };
 
 constexpr int kMaxFan = 8;
@@ -610,7 +615,14 @@ block_fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             ptx::fence_proxy_async_smem();
             const int cols = min(128, p.N - col0);  // N is a multiple of 8: whole 16-byte chunks
             if (flat < p.numel && cols > 0) {
-              ptx::bulk_store_1d(static_cast<OutT*>(p.C) + (int64_t)flat * p.ldc + col0, wstage + lane * L::kRowStride,
+              OutT* base = static_cast<OutT*>(p.C);
+              int local = flat;
+              if (p.scatter_rows_per_dest > 0) {
+                const int r = fast_div(flat, p.scatter_div);
+                base = static_cast<OutT*>(p.dest[r]);
+                local = flat - r * p.scatter_rows_per_dest;
+              }
+              ptx::bulk_store_1d(base + (int64_t)local * p.ldc + col0, wstage + lane * L::kRowStride,
                                  (uint32_t)cols * (uint32_t)sizeof(OutT));
               ptx::tma_store_commit();
             }

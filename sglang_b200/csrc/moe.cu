@@ -126,10 +126,16 @@ constexpr int kSumReduceMaxSlots = 64;
 template <typename T>
 __global__ void __launch_bounds__(256, 6) moe_sum_reduce_kernel(const T* __restrict__ y, const int32_t* __restrict__ topk_ids,
                                                                 T* __restrict__ out, int topk, int E, int64_t H, float scale,
-                                                                int skip_unrouted) {
+                                                                int skip_unrouted, const int* __restrict__ poison_status) {
   __shared__ int s_slot[kSumReduceMaxSlots];
   __shared__ int s_n;
   const int64_t t = blockIdx.x;
+  if (poison_status != nullptr && *reinterpret_cast<const volatile int*>(poison_status) != 0) {
+    // the rows were to be written by other GPUs and the handshake before this kernel gave up: NaNs, not stale rows
+    const uint4 nan16 = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);  // NaN in bf16 and fp16
+    for (int64_t c = threadIdx.x * 8; c < H; c += blockDim.x * 8) *reinterpret_cast<uint4*>(out + t * H + c) = nan16;
+    return;
+  }
   if (threadIdx.x < 32) {  // warp 0 compacts the valid slots, ascending (topk <= 64: two rounds of 32)
     int n = 0;
     for (int j0 = 0; j0 < topk; j0 += 32) {
@@ -342,11 +348,20 @@ static int run_fused_experts_decode(const void* hidden, const float* hidden_scal
   return check_launch("moe_sum_reduce_splits");
 }
 
+// Destinations of the (token, slot) rows when they leave for several buffers (expert-parallel combine by push).
+struct ScatterDests {
+  void* dest[8];
+  int n;
+  int64_t rows_per_dest;
+};
+
 template <typename T>
 static int run_fused_experts(const void* hidden, const float* hidden_scale, const void* w1, const void* w2, const float* w1_scale,
                              const float* w2_scale, const float* topk_weights, const int32_t* topk_ids, void* out,
                              int64_t T_tokens, int topk, int E, int64_t H, int64_t I, int combine_mode,
-                             int weight_on_input, float routed_scale, uint8_t* ws, cudaStream_t st) {
+                             int weight_on_input, float routed_scale, uint8_t* ws, cudaStream_t st,
+                             const ScatterDests* scatter = nullptr) {
+  if (scatter != nullptr) combine_mode = B200_COMBINE_NONE;  // rows leave per (token, slot); the receiver sums
   const int no_combine = combine_mode == B200_COMBINE_NONE;
   const int skip_unrouted = combine_mode == B200_COMBINE_SUM_SKIP_UNROUTED;
   const MoeWorkspace L = moe_workspace_layout(T_tokens, topk, E, H, I);
@@ -362,11 +377,12 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   // Opt-in (knob moe_decode = 1): measured slower than the tile path below at every token count tried (the
   // in-kernel row fetches sit behind the saturated weight stream in L2 and pace the pipeline, and more work
   // items than resident CTAs run in waves), so the tile path stays the default.
-  if (L.decode && tuning().moe_decode == 1)
+  if (L.decode && tuning().moe_decode == 1 && scatter == nullptr)
     return run_fused_experts_decode<T>(hidden, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, out, T_tokens,
                                        topk, E, H, I, combine_mode, weight_on_input, routed_scale, ws, L, st);
   int down_splits = L.down_splits;
   if (tuning().moe_down_splitk == 0) down_splits = 1;  // knob: keep the 16-bit single-pass path
+  if (scatter != nullptr) down_splits = 1;             // rows go straight to their receivers in 16 bits
   const bool split = down_splits > 1;
   T* c3 = no_combine && !split ? static_cast<T*>(out) : reinterpret_cast<T*>(ws + L.off_c3);
 
@@ -374,7 +390,7 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
                                      L.cap_blocks, npp, cumsum, 1, ws + L.off_align,
                                      b200_moe_align_workspace_bytes(numel, E + 1), st);
   if (rc) return rc;
-  if (no_combine && !split) {
+  if (no_combine && !split && scatter == nullptr) {
     // rows of slots whose expert is not on this rank are never written by GEMM 2
     cudaError_t e = cudaMemsetAsync(out, 0, (size_t)numel * H * sizeof(T), st);
     if (e != cudaSuccess) {
@@ -421,6 +437,12 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   // GEMM 2: [cap, I] x w2[E, H, I]^T -> rows scattered to (token, slot), times the router weight
   p.As = as2; p.as_sk = L.cap; p.Bs = w2_scale; p.C = c3; p.ldc = H; p.N = (int)H; p.K = (int)I;
   p.topk_weights = weight_on_input ? nullptr : topk_weights;
+  if (scatter != nullptr) {
+    p.C = nullptr;
+    p.scatter_rows_per_dest = (int)scatter->rows_per_dest;
+    p.scatter_div = make_fastdiv((int)scatter->rows_per_dest);
+    for (int d = 0; d < scatter->n; ++d) p.dest[d] = scatter->dest[d];
+  }
   if (split) {
     p.split_stride = numel * H;
     if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, float>(aq2, w2, (int64_t)E * H, p, 256, st, tiles_hint, down_splits)))
@@ -435,7 +457,7 @@ static int run_fused_experts(const void* hidden, const float* hidden_scale, cons
   if ((rc = launch_gemm<GEMM_GROUPED_SCATTER, T>(aq2, w2, (int64_t)E * H, p, force_bn, st, tiles_hint))) return rc;
   if (!no_combine) {
     moe_sum_reduce_kernel<T><<<(unsigned)T_tokens, 256, 0, st>>>(c3, topk_ids, static_cast<T*>(out), topk, E, H,
-                                                                  routed_scale, skip_unrouted);
+                                                                  routed_scale, skip_unrouted, nullptr);
     if ((rc = check_launch("moe_sum_reduce"))) return rc;
   }
   return B200_OK;
@@ -581,4 +603,77 @@ extern "C" int b200_fused_experts_fp8(const void* hidden, const float* hidden_sc
                                      no_combine, apply_router_weight_on_input, routed_scaling_factor, ws, st);
   set_error_detail("fused_experts: hidden dtype code %d is not bf16/f16", h_dtype);
   return B200_E_UNSUPPORTED;
+}
+
+extern "C" int b200_fused_experts_fp8_scatter(const void* hidden_q, const float* hidden_scale, int out_dtype, const void* w1,
+                                              const void* w2, const float* w1_scale, const float* w2_scale,
+                                              const float* topk_weights, const int32_t* topk_ids, void* const* dests,
+                                              int n_dest, int64_t rows_per_dest, int64_t T, int topk, int E, int64_t H,
+                                              int64_t I, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(T >= 0 && topk > 0 && E > 0 && H > 0 && I > 0, "fused_experts_scatter: bad shape");
+  if (T == 0) return B200_OK;
+  B200_CHECK_ARG(hidden_q && hidden_scale && w1 && w2 && w1_scale && w2_scale && topk_weights && topk_ids && dests,
+                 "fused_experts_scatter: null pointer (rows arrive quantised: FP8 bytes + scales)");
+  B200_CHECK_ARG(n_dest >= 1 && n_dest <= 8 && rows_per_dest > 0 && rows_per_dest < (1LL << 30) &&
+                     (int64_t)n_dest * rows_per_dest >= T * topk,
+                 "fused_experts_scatter: %d destinations x %lld rows do not cover %lld pairs", n_dest,
+                 (long long)rows_per_dest, (long long)(T * topk));
+  B200_UNSUPPORTED(H % 128 != 0 || I % 128 != 0, "fused_experts_scatter: H=%lld and I=%lld must be multiples of 128",
+                   (long long)H, (long long)I);
+  B200_UNSUPPORTED(E + 1 > 1025, "fused_experts_scatter: more than 1024 experts");
+  B200_UNSUPPORTED(T * topk >= (1LL << 30), "fused_experts_scatter: too many (token, slot) pairs");
+  ScatterDests sd = {};
+  sd.n = n_dest;
+  sd.rows_per_dest = rows_per_dest;
+  for (int d = 0; d < n_dest; ++d) {
+    B200_CHECK_ARG(dests[d] && ((uintptr_t)dests[d] & 15) == 0, "fused_experts_scatter: destination %d null or unaligned", d);
+    sd.dest[d] = dests[d];
+  }
+  B200_CHECK_ARG(((uintptr_t)hidden_q & 15) == 0 && ((uintptr_t)w1 & 15) == 0 && ((uintptr_t)w2 & 15) == 0,
+                 "fused_experts_scatter: tensors must be 16-byte aligned");
+  const size_t need = b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0) {
+    set_error_detail("fused_experts_scatter: workspace %zu < %zu bytes or not 256-byte aligned", workspace_bytes, need);
+    return B200_E_WORKSPACE;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (out_dtype == B200_BF16)
+    return run_fused_experts<__nv_bfloat16>(hidden_q, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, nullptr, T,
+                                            topk, E, H, I, B200_COMBINE_NONE, 0, 1.0f, ws, st, &sd);
+  if (out_dtype == B200_F16)
+    return run_fused_experts<__half>(hidden_q, hidden_scale, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, nullptr, T, topk,
+                                     E, H, I, B200_COMBINE_NONE, 0, 1.0f, ws, st, &sd);
+  set_error_detail("fused_experts_scatter: output dtype code %d is not bf16/f16", out_dtype);
+  return B200_E_UNSUPPORTED;
+}
+
+extern "C" int b200_moe_sum_reduce(const void* rows, const int32_t* topk_ids, void* out, int dtype, int64_t T, int topk, int E,
+                                   int64_t H, float scale, int skip_unrouted, int poison_on_status, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(T >= 0 && topk > 0 && E > 0 && H > 0 && H % 8 == 0, "moe_sum_reduce: bad shape");
+  if (T == 0) return B200_OK;
+  B200_CHECK_ARG(rows && topk_ids && out && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)out & 15) == 0,
+                 "moe_sum_reduce: null or unaligned pointer");
+  B200_UNSUPPORTED(topk > kSumReduceMaxSlots, "moe_sum_reduce: more than %d experts per token", kSumReduceMaxSlots);
+  B200_UNSUPPORTED(T >= (1LL << 31), "moe_sum_reduce: too many tokens");
+  const int* status = poison_on_status ? device_status_word() : nullptr;
+  if (poison_on_status && !status) {
+    set_error_detail("cannot resolve the device status word");
+    return B200_E_LAUNCH;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_BF16)
+    moe_sum_reduce_kernel<__nv_bfloat16><<<(unsigned)T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(rows), topk_ids,
+                                                                       static_cast<__nv_bfloat16*>(out), topk, E, H, scale,
+                                                                       skip_unrouted, status);
+  else if (dtype == B200_F16)
+    moe_sum_reduce_kernel<__half><<<(unsigned)T, 256, 0, st>>>(static_cast<const __half*>(rows), topk_ids,
+                                                                static_cast<__half*>(out), topk, E, H, scale, skip_unrouted, status);
+  else {
+    set_error_detail("moe_sum_reduce: dtype code %d is not bf16/f16", dtype);
+    return B200_E_UNSUPPORTED;
+  }
+  return check_launch("moe_sum_reduce");
 }

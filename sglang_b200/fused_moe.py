@@ -134,6 +134,62 @@ def fused_experts_impl(
     return out
 
 
+def fused_experts_scatter(
+    rows_q: torch.Tensor, rows_scale: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor, w1_scale: torch.Tensor, w2_scale: torch.Tensor, dest_ptrs, rows_per_dest: int,
+    output_dtype: torch.dtype = torch.bfloat16,
+) -> None:
+    """Experts of this rank over ``T`` positions of already quantised rows (``rows_q [T, H]`` e4m3,
+    ``rows_scale [T, H/128]``, ``topk_ids`` local to this rank with -1 for "not mine"), router weight applied
+    and NO slot sum: the down GEMM sends the row of pair ``t * topk + j`` into buffer
+    ``dest_ptrs[(t * topk + j) // rows_per_dest]`` (a ``ctypes`` array of device pointers, peer memory allowed)
+    at row ``(t * topk + j) % rows_per_dest``. The combine half of an expert-parallel layer
+    (python/sglang/srt/layers/moe/token_dispatcher/deepep.py:560-602) done by the GEMM's own epilogue."""
+    N.require_cuda(rows_q, rows_scale, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale)
+    T, H = rows_q.shape
+    E, two_i, _ = w1.shape
+    I = two_i // 2
+    topk = topk_ids.shape[1]
+    assert rows_q.dtype == fp8_dtype and rows_q.is_contiguous() and rows_scale.dtype == torch.float32
+    assert rows_scale.is_contiguous() and tuple(rows_scale.shape) == (T, H // 128)
+    assert topk_weights.dtype == torch.float32 and topk_ids.dtype == torch.int32
+    assert topk_weights.is_contiguous() and topk_ids.is_contiguous() and tuple(topk_weights.shape) == (T, topk)
+    assert w1.dtype == fp8_dtype and w2.dtype == fp8_dtype and w1.is_contiguous() and w2.is_contiguous()
+    assert w2.shape == (E, H, I)
+    w1_scale = w1_scale.to(torch.float32).contiguous()
+    w2_scale = w2_scale.to(torch.float32).contiguous()
+    if T == 0:
+        return
+    lib = N.load()
+    ws_bytes = lib.b200_fused_experts_fp8_workspace_bytes(T, topk, E, H, I)
+    with N.on_device(rows_q):
+        ws = _workspace(rows_q.device, ws_bytes)
+        st = lib.b200_fused_experts_fp8_scatter(
+            N.ptr(rows_q), N.ptr(rows_scale), N.DTYPE_CODE[output_dtype], N.ptr(w1), N.ptr(w2), N.ptr(w1_scale),
+            N.ptr(w2_scale), N.ptr(topk_weights), N.ptr(topk_ids), dest_ptrs, len(dest_ptrs), rows_per_dest, T, topk, E, H, I,
+            N.ptr(ws), ws_bytes, N.current_stream(),
+        )
+    N.check(st, "fused_experts_scatter")
+
+
+def moe_sum_reduce(rows: torch.Tensor, topk_ids: torch.Tensor, out: torch.Tensor, num_experts: int,
+                   routed_scaling_factor: float = 1.0, skip_unrouted_rows: bool = False,
+                   poison_on_status: bool = False) -> torch.Tensor:
+    """``out[t] = routed_scaling_factor * sum_j rows[t, j]`` over the slots whose id is in ``[0, num_experts)``
+    (fp32 sum in slot order; the last step of ``fused_experts``, fused_moe.py:726-745). ``rows [T, topk, H]``.
+    ``poison_on_status``: fill ``out`` with NaN when the device status word reports an expired wait."""
+    N.require_cuda(rows, topk_ids, out)
+    T, topk, H = rows.shape
+    assert rows.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, H) and out.dtype == rows.dtype
+    assert topk_ids.dtype == torch.int32 and topk_ids.is_contiguous() and tuple(topk_ids.shape) == (T, topk)
+    with N.on_device(rows):
+        st = N.load().b200_moe_sum_reduce(N.ptr(rows), N.ptr(topk_ids), N.ptr(out), N.DTYPE_CODE[rows.dtype], T, topk,
+                                          num_experts, H, float(routed_scaling_factor), int(skip_unrouted_rows),
+                                          int(poison_on_status), N.current_stream())
+    N.check(st, "moe_sum_reduce")
+    return out
+
+
 def fused_experts(
     hidden_states: torch.Tensor,
     w1: torch.Tensor,

@@ -237,12 +237,13 @@ class FusedMoE:
 
     def __init__(self, w1, w2, w1_s, w2_s, rank: int, size: int, mode: str = "ep", group=None,
                  expert_fn: Optional[Callable] = None, presharded: bool = False, num_experts: Optional[int] = None,
-                 max_tokens: int = 8192):
+                 max_tokens: int = 8192, peer_combine: str = "push"):
         """``presharded``: the four tensors are already this rank's shard (a loader that never
         materialises the full layer); ``num_experts`` then gives the global expert count."""
         assert mode in ("tp", "ep", "ep_a2a", "ep_peer")
         self.mode, self.rank, self.size, self.group = mode, rank, size, group
-        self.max_tokens, self._peer = max_tokens, None
+        assert peer_combine in ("push", "pull")
+        self.max_tokens, self._peer, self.peer_combine = max_tokens, None, peer_combine
         if presharded:
             self.num_experts = num_experts if num_experts is not None else w1.shape[0] * (1 if mode == "tp" else size)
             self.w1, self.w2, self.w1_s, self.w2_s = w1, w2, w1_s, w2_s
@@ -281,7 +282,14 @@ class FusedMoE:
                 fused_experts_impl(q, self.w1, self.w2, w, ids, self.w1_s, self.w2_s, inplace=False,
                                    hidden_states_scale=s, output_dtype=out.dtype, out=out, skip_unrouted_rows=True)
 
-            return self._peer.forward(hidden_states, topk_weights, topk_ids, experts)
+            def experts_scatter(q, s, w, ids, dest_ptrs, rows_per_dest):
+                from .fused_moe import fused_experts_scatter
+
+                fused_experts_scatter(q, s, self.w1, self.w2, w, ids, self.w1_s, self.w2_s, dest_ptrs, rows_per_dest,
+                                      hidden_states.dtype)
+
+            return self._peer.forward(hidden_states, topk_weights, topk_ids, experts,
+                                      experts_scatter if self.peer_combine == "push" else None)
         from .fp8_kernel import per_token_group_quant_fp8
 
         quant = getattr(self, "_quant_fn", None) or (lambda t: per_token_group_quant_fp8(t, 128))

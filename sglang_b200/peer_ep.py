@@ -10,6 +10,12 @@ Every rank holds a receive area indexed by (source rank, source token position) 
   into this rank's output area -> handshake -> ``b200_ep_combine`` (peer loads of the partial
   rows from the owners' output areas, fp32 sum at the source).
 
+With ``experts_scatter`` (what ``parallel.FusedMoE`` passes) the combine is a push fused into the owners'
+down GEMM: its epilogue sends every finished (token, slot) row straight into the SOURCE rank's inbox
+``[T_max * topk, H]`` while the remaining tiles are still being multiplied, and after the second handshake the
+source sums its slots locally -- the combine traffic overlaps the GEMM instead of following it (at 8 ranks the
+pull cost 0.15 ms after a 0.06 ms pre-reduction on the owner).
+
 It replaces the DeepEP normal-mode dispatch / combine the reference uses for this exchange
 (python/sglang/srt/layers/moe/token_dispatcher/deepep.py:507-602).
 
@@ -54,7 +60,8 @@ class PeerExpertParallel:
         self.off_w = up(self.off_s + pos * (hidden // 128) * 4)
         self.off_ids = up(self.off_w + pos * topk * 4)
         self.off_out = up(self.off_ids + pos * topk * 4)
-        self.off_flags = up(self.off_out + pos * hidden * 2)
+        self.off_inbox = up(self.off_out + pos * hidden * 2)  # [T_max * topk, H]: rows pushed by the owners
+        self.off_flags = up(self.off_inbox + max_tokens * topk * hidden * 2)
         total = self.off_flags + 256
         dev = torch.device("cuda", torch.cuda.current_device())
         self.buf = symm.empty(total, dtype=torch.uint8, device=dev)
@@ -73,6 +80,7 @@ class PeerExpertParallel:
         self._recv_ids = arr(*[b + self.off_ids for b in self.base])
         self._peer_out = arr(*[b + self.off_out for b in self.base])
         self._peer_flags = arr(*[b + self.off_flags for b in self.base])
+        self._peer_inbox = arr(*[b + self.off_inbox for b in self.base])
         # this rank's areas as tensors
         b = self.buf
         self.q = b[self.off_q : self.off_q + pos * hidden].view(fp8_dtype).view(pos, hidden)
@@ -80,6 +88,7 @@ class PeerExpertParallel:
         self.w = b[self.off_w : self.off_w + pos * topk * 4].view(torch.float32).view(pos, topk)
         self.ids = b[self.off_ids : self.off_ids + pos * topk * 4].view(torch.int32).view(pos, topk)
         self.out = b[self.off_out : self.off_out + pos * hidden * 2].view(dtype).view(pos, hidden)
+        self.inbox = b[self.off_inbox : self.off_inbox + max_tokens * topk * hidden * 2].view(dtype).view(max_tokens, topk, hidden)
 
     def _handshake(self, phase: int, stream: int) -> None:
         st = N.load().b200_peer_handshake(self.base[self.rank] + self.off_flags, self._peer_flags, self.world, self.rank,
@@ -97,10 +106,13 @@ class PeerExpertParallel:
                                "another GPU ran out; results since the last check are invalid (filled with NaN)")
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
-                experts: Callable[[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor], None]):
+                experts: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor], None]],
+                experts_scatter: Optional[Callable] = None):
         """``hidden_states [T, H]`` (T <= max_tokens) local tokens with GLOBAL ``topk_ids``;
         ``experts(q, s, w, local_ids, out)`` runs this rank's experts over the receive area and
-        writes ``out``. Returns ``[T, H]``."""
+        writes ``out`` (combine by pull), or ``experts_scatter(q, s, w, local_ids, dest_ptrs, rows_per_dest)``
+        runs them and sends every (token, slot) row to its source rank's inbox (combine by push, taken when
+        given). Returns ``[T, H]``."""
         N.require_cuda(hidden_states, topk_weights, topk_ids)
         T, H = hidden_states.shape
         assert H == self.H and T <= self.T_max and topk_ids.shape == (T, self.k), "sized for other shapes"
@@ -117,6 +129,14 @@ class PeerExpertParallel:
                                       stream)
             N.check(st, "ep_dispatch")
             self._handshake(0, stream)
+            if experts_scatter is not None:
+                # position s * T_max + t, slot j -> pair (s * T_max + t) * k + j: inbox of rank s, row t * k + j
+                experts_scatter(self.q, self.s, self.w, self.ids, self._peer_inbox, self.T_max * self.k)
+                self._handshake(1, stream)
+                from .fused_moe import moe_sum_reduce
+
+                moe_sum_reduce(self.inbox[:T], ti, result, self.E, poison_on_status=True)
+                return result
             experts(self.q, self.s, self.w, self.ids, self.out)
             self._handshake(1, stream)
             st = lib.b200_ep_combine(self._peer_out, N.ptr(ti), N.ptr(result), N.DTYPE_CODE[self.dtype], T, self.T_max,

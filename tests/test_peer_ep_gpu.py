@@ -79,6 +79,71 @@ def test_dispatch_experts_combine_emulated_ranks(p, E, k, H, I, T_max, tokens):
     assert N.read_device_status() == 0
 
 
+@pytest.mark.parametrize("p,E,k,H,I,T_max,tokens", [(2, 8, 2, 256, 128, 40, [37, 40]), (4, 16, 4, 512, 256, 24, [24, 1, 0, 17]),
+                                                   (8, 32, 8, 256, 128, 12, [12, 3, 0, 7, 12, 1, 9, 5]), (1, 8, 2, 256, 128, 16, [9])])
+def test_dispatch_experts_push_combine_emulated_ranks(p, E, k, H, I, T_max, tokens):
+    """Combine by push: the down GEMM of every owner sends its (token, slot) rows into the source rank's inbox
+    (here: p inboxes on one GPU), then each source sums its slots. Inboxes start as NaN, so a row sent to the
+    wrong place or not at all shows up."""
+    import sglang_b200 as S
+    from sglang_b200 import _native as N
+    from sglang_b200.fused_moe import fused_experts_scatter, moe_sum_reduce
+
+    lib = N.load()
+    g = torch.Generator().manual_seed(p * 1000 + E)
+    w1 = torch.stack([O.block_quant_weight_fp8((torch.randn(2 * I, H, generator=g) * 0.02).bfloat16())[0] for _ in range(E)])
+    w2 = torch.stack([O.block_quant_weight_fp8((torch.randn(H, I, generator=g) * 0.02).bfloat16())[0] for _ in range(E)])
+    w1_s = torch.rand(E, 2 * I // 128, H // 128, generator=g) * 2e-4 + 1e-4
+    w2_s = torch.rand(E, H // 128, I // 128, generator=g) * 2e-4 + 1e-4
+    pos = p * T_max
+    dev = "cuda"
+    q = [torch.full((pos, H), 0x7F, dtype=torch.uint8, device=dev) for _ in range(p)]
+    s = [torch.full((pos, H // 128), float("nan"), device=dev) for _ in range(p)]
+    w = [torch.full((pos, k), float("nan"), device=dev) for _ in range(p)]
+    ids = [torch.full((pos, k), 12345, dtype=torch.int32, device=dev) for _ in range(p)]
+    inbox = [torch.full((T_max, k, H), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(p)]
+    xs, tws, tis = [], [], []
+    for r in range(p):
+        T = tokens[r]
+        x = torch.randn(T, H, generator=g).bfloat16()
+        tw, ti = O.softmax_topk(torch.randn(T, E, generator=g), k, True)
+        if T > 3:
+            ti[1, 0] = -1  # an id that belongs to nobody: its inbox row stays NaN and must not be summed
+        xs.append(x); tws.append(tw); tis.append(ti)
+        xq, xsc = S.per_token_group_quant_fp8(x.cuda(), 128) if T else (torch.empty(0, H, dtype=torch.float8_e4m3fn, device=dev), torch.empty(0, H // 128, device=dev))
+        tw_d, ti_d = tw.cuda(), ti.cuda()
+        N.check(lib.b200_ep_dispatch(N.ptr(xq), N.ptr(xsc), N.ptr(tw_d), N.ptr(ti_d), T, T_max, k, H, E, p, r,
+                                     _arr(q), _arr(s), _arr(w), _arr(ids), N.current_stream()), "dispatch")
+        torch.cuda.synchronize()
+    per = E // p
+    dests = _arr(inbox)
+    for d in range(p):
+        lo = d * per
+        fused_experts_scatter(q[d].view(torch.float8_e4m3fn), s[d], w1[lo : lo + per].cuda(), w2[lo : lo + per].cuda(), w[d],
+                              ids[d], w1_s[lo : lo + per].cuda(), w2_s[lo : lo + per].cuda(), dests, T_max * k, torch.bfloat16)
+        torch.cuda.synchronize()
+    for r in range(p):
+        T = tokens[r]
+        if T == 0:
+            assert bool(torch.isnan(inbox[r]).all())  # nobody writes into the inbox of a rank without tokens
+            continue
+        res = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        moe_sum_reduce(inbox[r][:T], tis[r].cuda().to(torch.int32), res, E, poison_on_status=True)
+        torch.cuda.synchronize()
+        valid = (tis[r] >= 0).cuda()
+        got_rows = ~torch.isnan(inbox[r][:T].float()).any(dim=2)
+        assert torch.equal(got_rows, valid), "exactly the rows of valid pairs arrive"
+        assert bool(torch.isnan(inbox[r][T:]).all())
+        ref = O.fused_experts_fp8(xs[r], w1, w2, w1_s, w2_s, tws[r], tis[r], [128, 128])
+        assert not torch.isnan(res.float()).any()
+        assert O.rel_frobenius(res.float().cpu(), ref) < TOL, r
+    assert N.read_device_status() == 0
+    # argument checks of the new entry points
+    assert lib.b200_fused_experts_fp8_scatter(None, None, N.BF16, None, None, None, None, None, None, dests, p, T_max * k, 4, k,
+                                              per, H, I, None, 0, None) == N.E_BAD_ARG
+    assert lib.b200_moe_sum_reduce(None, None, None, N.BF16, 4, k, E, H, 1.0, 0, 0, None) == N.E_BAD_ARG
+
+
 def test_handshake_with_itself_and_argument_checks():
     from sglang_b200 import _native as N
 
