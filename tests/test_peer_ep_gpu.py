@@ -211,6 +211,17 @@ def _silent_peer_case(lib, N):
     N.check(lib.b200_ep_combine(areas, ids.data_ptr(), res.data_ptr(), N.BF16, 4, 4, 2, 256, 8, 2, 0, N.current_stream()),
             "combine")
     assert N.read_device_status() == 2 and bool(torch.isnan(res).all())
+    # the same for the push form: the source's slot sum after a handshake that gave up
+    inbox = torch.ones(4, 2, 256, dtype=torch.bfloat16, device="cuda")
+    res2 = torch.full((4, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    N.check(lib.b200_peer_handshake(mine.data_ptr(), peers, 2, 0, 1, 10, N.current_stream()), "handshake")
+    N.check(lib.b200_moe_sum_reduce(inbox.data_ptr(), ids.data_ptr(), res2.data_ptr(), N.BF16, 4, 2, 8, 256, 1.0, 0, 1,
+                                    N.current_stream()), "sum_reduce")
+    assert N.read_device_status() == 2 and bool(torch.isnan(res2).all())
+    # and with a clear status word the same call sums: two slots of ones
+    N.check(lib.b200_moe_sum_reduce(inbox.data_ptr(), ids.data_ptr(), res2.data_ptr(), N.BF16, 4, 2, 8, 256, 1.0, 0, 1,
+                                    N.current_stream()), "sum_reduce")
+    assert N.read_device_status() == 0 and bool(torch.all(res2 == 2.0))
     # the context is intact: a healthy single-rank call right after
     flags = torch.zeros(64, dtype=torch.int32, device="cuda")
     self_only = (ctypes.c_void_p * 1)(flags.data_ptr())
