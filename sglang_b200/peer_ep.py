@@ -23,7 +23,8 @@ Buffer reuse needs no double buffering: a rank starts the dispatch of call n+1 o
 combine of call n, i.e. after the second handshake of call n, which every owner enters after its
 experts of call n have finished reading the receive area; and an owner starts writing outputs of
 call n+1 only after the first handshake of call n+1, which every source enters after its combine
-of call n."""
+of call n. The same holds for the inbox of the push form: owners write it in their down GEMM of call
+n+1, i.e. after the first handshake of call n+1, which the source enters after its slot sum of call n."""
 from __future__ import annotations
 
 import ctypes
