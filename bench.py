@@ -960,10 +960,14 @@ def bench_moe_parallel(S, device, rank: int, world: int, steps: int, fp8_peak: f
                     continue
                 ms = timed(lambda: layer(xs, ws_, is_), max(2, steps // 2), world, device)
                 # per GPU: 1/world of the flops, its experts' weights once; the all-to-all forms move every local
-                # token's FP8 row + scales to the other owning ranks and bf16 partial rows back (at most
-                # topk_group ranks per token); the standard form all-reduces the [T, H] bf16 output
+                # token's FP8 row + scales to the other owning ranks (at most topk_group ranks per token) and bf16
+                # rows back (one partial row per owning rank, or one row per slot when the down GEMM pushes
+                # them); the standard form all-reduces the [T, H] bf16 output
                 if mode == "ep":
                     link = 2 * (world - 1) / world * T * H * 2
+                elif mode == "ep_peer":
+                    # rows out once per owning rank; results back once per (token, slot): pushed by the down GEMM
+                    link = per * (world - 1) / world * (min(cfg["topk_group"], world) * (H + H // 32) + topk * 2 * H)
                 else:
                     link = per * min(cfg["topk_group"], world) * (world - 1) / world * (H + H // 32 + 2 * H)
                 active = int(torch.unique(ti).numel())
