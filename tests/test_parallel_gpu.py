@@ -68,6 +68,12 @@ def _worker(rank, world, port, results):
             outs.append((sl, peer(xm[sl].cuda(), tw[sl].cuda(), ti[sl].cuda()).clone()))
         for rep, (sl, out) in enumerate(outs):
             res[f"ep_peer_{rep}"] = O.rel_frobenius(out.float().cpu(), ref[sl])
+        # the pull form of the combine (owner pre-reduces, source pulls with peer loads)
+        pull = P.FusedMoE(*dev, rank, world, mode="ep_peer", max_tokens=per + 3, peer_combine="pull")
+        dist.barrier()
+        sl = slice(rank * per, rank * per + per - 2)
+        out = pull(xm[sl].cuda(), tw[sl].cuda(), ti[sl].cuda())
+        res["ep_peer_pull"] = O.rel_frobenius(out.float().cpu(), ref[sl])
         res["status"] = _native.read_device_status()
         results[rank] = res
     finally:
